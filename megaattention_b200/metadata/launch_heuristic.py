@@ -1,0 +1,68 @@
+"""Launch heuristic: role weights and super-group size from the FA / O_proj MAC ratio.
+
+Mirror of the reference ``src/mega_attention/metadata/launch_heuristic.py``
+(``estimate_work_ratio`` :21-25, ``LaunchConfig`` :28-33, ``choose_launch_config``
+:36-47).  Outputs are bit-identical to the reference, including its two quirks:
+the ratio counts ``m_block + 1`` KV blocks per tile and so ignores any KV prefix of
+chunked prefill, and ``num_sms`` is accepted but unused.
+
+``choose_launch_config_b200`` is an additional entry point (no reference counterpart)
+that accounts for the KV prefix; the reference-compatible function is left untouched.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from .row_desc import cdiv
+
+# Ratio at which the table switches from the balanced row to the FA-heavy row.
+_R_LO = 2.0
+# (w_fa, w_oproj, sg) below / at-or-above the switch point.
+_TABLE = ((2, 1, 4), (8, 1, 4))
+
+
+def estimate_work_ratio(meta, hidden: int, N_TILE: int = 128) -> float:
+    """``2 * sum(m_block + 1) / (num_row_tiles * ceil(hidden / N_TILE))``.
+
+    The integer sum is taken in int64 and the quotient is one Python true division,
+    which is what makes the value reproducible bit for bit.
+    """
+    kv_blocks = int(np.add.reduce(meta.m_block.astype(np.int64) + 1))
+    return (2 * kv_blocks) / (meta.num_row_tiles * cdiv(hidden, N_TILE))
+
+
+@dataclass
+class LaunchConfig:
+    w_fa: int
+    w_oproj: int
+    w_ar: int
+    sg: int
+
+
+def choose_launch_config(meta, hidden: int, tp_size: int,
+                         N_TILE: int = 128, num_sms: int = 132) -> LaunchConfig:
+    """Two-bucket table lookup on the work ratio; ``w_ar`` is 0 on a single rank."""
+    row = _TABLE[0] if estimate_work_ratio(meta, hidden, N_TILE) < _R_LO else _TABLE[1]
+    sg = max(1, min(row[2], cdiv(hidden, N_TILE)))
+    return LaunchConfig(w_fa=row[0], w_oproj=row[1], w_ar=int(tp_size > 1), sg=sg)
+
+
+def estimate_work_ratio_kv(meta, hidden: int, N_TILE: int = 128) -> float:
+    """Work ratio that counts the KV blocks a tile really visits (prefix included)."""
+    M = meta.M_TILE
+    b = meta.batch_idx.astype(np.int64)
+    lq = np.diff(meta.cu_seqlens_q.astype(np.int64))[b]
+    lk = np.diff(meta.cu_seqlens_k.astype(np.int64))[b]
+    last_row = (meta.m_block.astype(np.int64) + 1) * M + (lk - lq)
+    nblk = np.minimum(-(-lk // M), -(-last_row // M))
+    return (2 * int(nblk.sum())) / (meta.num_row_tiles * cdiv(hidden, N_TILE))
+
+
+def choose_launch_config_b200(meta, hidden: int, tp_size: int,
+                              N_TILE: int = 128) -> LaunchConfig:
+    """Same table, indexed by the KV-aware ratio.  Not part of the reference surface."""
+    row = _TABLE[0] if estimate_work_ratio_kv(meta, hidden, N_TILE) < _R_LO else _TABLE[1]
+    sg = max(1, min(row[2], cdiv(hidden, N_TILE)))
+    return LaunchConfig(w_fa=row[0], w_oproj=row[1], w_ar=int(tp_size > 1), sg=sg)

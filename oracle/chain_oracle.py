@@ -1,0 +1,123 @@
+"""CPU oracle for the fused prefill path.  TEST INFRASTRUCTURE ONLY — never on a
+product code path; it is the checker, not the thing measured or shipped.
+
+Restates, in explicit fp32 tensor arithmetic, the algorithm of the reference's
+``src/mega_attention/reference/fused.py``:
+
+* ``fa_oracle``        follows ``fa_reference``        (fused.py:80-117)
+* ``o_scratch_oracle`` follows ``o_scratch_reference`` (fused.py:178-193)
+* ``oproj_oracle``     follows ``oproj_reference``     (fused.py:197-204)
+* ``allreduce_oracle`` follows ``allreduce_reference`` (fused.py:207-212) with the
+  cross-rank sum taken over a list of per-rank partials instead of a process group
+* ``full_chain_oracle`` follows ``full_chain_reference`` (fused.py:215-221)
+
+The reference delegates the attention math to ``torch.nn.functional.
+scaled_dot_product_attention`` (PyTorch, unpinned in the reference's pyproject; 2.11.0
+in this image) with an explicit boolean mask on fp32 tensors.  Here the published
+definition is written out: ``softmax(scale * Q K^T + mask) V`` with the mask keeping
+``kpos <= qpos + (k_len - q_len)`` (causal, aligned bottom-right).
+
+Parity pin: ``tests/golden/*.npz`` hold outputs of the reference module itself
+(imported from the reference tree by ``tests/golden/make_golden.py``); the CPU tests
+check this file against them.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+M_TILE = 128
+
+
+def _cu(lens):
+    out = np.zeros(len(lens) + 1, dtype=np.int64)
+    out[1:] = np.cumsum(np.asarray(lens, dtype=np.int64))
+    return out
+
+
+def fa_oracle(Q, K, V, seqlens_q, seqlens_k=None, softmax_scale=None):
+    """Causal varlen GQA attention in fp32.
+
+    ``Q [tot_q, H, D]``, ``K/V [tot_k, H_kv, D]`` packed per sequence; q head ``h`` reads
+    kv head ``h // (H // H_kv)``.  Returns ``O [tot_q, H, D]`` fp32.
+    """
+    seqlens_k = seqlens_q if seqlens_k is None else seqlens_k
+    H, Hkv, D = Q.shape[1], K.shape[1], Q.shape[2]
+    assert H % Hkv == 0
+    group = H // Hkv
+    scale = float(D) ** -0.5 if softmax_scale is None else float(softmax_scale)
+    cq, ck = _cu(seqlens_q), _cu(seqlens_k)
+    O = torch.zeros(Q.shape, dtype=torch.float32)
+    for b in range(len(seqlens_q)):
+        q0, q1, k0, k1 = int(cq[b]), int(cq[b + 1]), int(ck[b]), int(ck[b + 1])
+        lq, lk = q1 - q0, k1 - k0
+        if lq == 0:
+            continue
+        keep = (torch.arange(lk)[None, :] <= torch.arange(lq)[:, None] + (lk - lq))
+        for h in range(H):
+            q = Q[q0:q1, h].float()
+            k = K[k0:k1, h // group].float()
+            v = V[k0:k1, h // group].float()
+            s = (q @ k.T) * scale
+            s = s.masked_fill(~keep, float("-inf"))
+            s = s - s.max(dim=1, keepdim=True).values
+            p = torch.exp(s)
+            O[q0:q1, h] = (p / p.sum(dim=1, keepdim=True)) @ v
+    return O
+
+
+def tile_coords(seqlens_q):
+    """``(q_tile_start, valid_m)`` per flattened 128-row tile (row_desc.py:96-104)."""
+    out = []
+    cq = _cu(seqlens_q)
+    for b, lq in enumerate(seqlens_q):
+        for mb in range(-(-int(lq) // M_TILE)):
+            out.append((int(cq[b]) + mb * M_TILE, min(M_TILE, int(lq) - mb * M_TILE)))
+    return out
+
+
+def o_scratch_oracle(O, seqlens_q):
+    """Pack ``O [tot_q,H,D]`` into ``[num_row_tiles,128,H,D]``; tail rows stay zero."""
+    tiles = tile_coords(seqlens_q)
+    out = torch.zeros(len(tiles), M_TILE, O.shape[1], O.shape[2], dtype=torch.float32)
+    for t, (start, vm) in enumerate(tiles):
+        out[t, :vm] = O[start:start + vm]
+    return out
+
+
+def oproj_oracle(O, W_o):
+    """``Y_partial [tot_q, hidden] = concat_heads(O) @ W_o`` in fp32; ``W_o [H*D, hidden]``."""
+    return O.float().reshape(O.shape[0], -1) @ W_o.float()
+
+
+def allreduce_oracle(partials):
+    """fp32 sum over the per-rank partials, then one cast to bf16."""
+    acc = partials[0].float().clone()
+    for p in partials[1:]:
+        acc += p.float()
+    return acc.to(torch.bfloat16)
+
+
+def full_chain_oracle(Q, K, V, W_o, seqlens_q, seqlens_k=None, softmax_scale=None):
+    """One rank: returns ``(O fp32, Y_partial fp32, Y_final bf16)``."""
+    O = fa_oracle(Q, K, V, seqlens_q, seqlens_k, softmax_scale)
+    Yp = oproj_oracle(O, W_o)
+    return O, Yp, allreduce_oracle([Yp])
+
+
+def untile_csym(csym, seqlens_q, hidden):
+    """``csym [R,128,num_out,128]`` -> ``[tot_q, hidden]`` over the valid region
+    (the de-tiling of benchmarks/bench_fused_fa_oproj_ar.py:263-269)."""
+    tiles = tile_coords(seqlens_q)
+    R, _, num_out, nt = csym.shape
+    flat = csym.reshape(R, M_TILE, num_out * nt)
+    out = torch.empty(int(sum(int(x) for x in seqlens_q)), hidden, dtype=csym.dtype)
+    for t, (start, vm) in enumerate(tiles):
+        out[start:start + vm] = flat[t, :vm, :hidden]
+    return out
+
+
+def err_rel(got, ref):
+    """``max|got - ref| / max|ref|`` in fp32 (bench_fused_fa_oproj_ar.py:259-270)."""
+    g, r = got.float(), ref.float()
+    return float((g - r).abs().max() / r.abs().max().clamp_min(1e-30))
