@@ -1,0 +1,120 @@
+/*
+ * C ABI of the B200 (sm_100a) fused prefill path:
+ *   causal varlen GQA FlashAttention -> row-parallel O_proj GEMM -> tensor-parallel
+ *   AllReduce, one persistent kernel, one 128-row tile as the unit of work.
+ *
+ * The reference project exposes this path only as Python objects; each entry point
+ * below names the reference interface it stands in for (path:line inside the reference
+ * tree).  Plain pointers and sizes only: device addresses travel as uint64_t, the
+ * stream as an opaque pointer (a cudaStream_t).  Every function returns 0 on success or
+ * a negative ma_error code; nothing throws and nothing exits the process.
+ *
+ * The library never allocates or frees the caller's buffers.  A plan borrows every
+ * device pointer it is given; they must stay valid until ma_plan_destroy.
+ */
+#ifndef MEGAATTN_B200_H_
+#define MEGAATTN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MA_MAX_TP 8
+#define MA_NUM_CTRL 8     /* src/mega_attention/kernels/sm90/fused_fa_oproj_ar.py:47-55 */
+#define MA_NUM_SYNC 3     /* fused_fa_oproj_ar.py:64-67 */
+#define MA_NUM_ACTV 6     /* src/mega_attention/metadata/row_desc.py:156-174 */
+#define MA_NUM_STATUS 8   /* device status block (no reference counterpart) */
+
+typedef enum ma_error {
+  MA_OK = 0,
+  MA_ERR_INVALID = -1,        /* bad argument / unsupported shape                      */
+  MA_ERR_CUDA = -2,           /* a CUDA runtime or driver call failed                  */
+  MA_ERR_NOT_SM100 = -3,      /* device is not compute capability 10.x                 */
+  MA_ERR_DEVICE_TIMEOUT = -4, /* a bounded device-side wait gave up (see ma_status)    */
+  MA_ERR_CAPACITY = -5        /* request exceeds a stated maximum                      */
+} ma_error;
+
+/* ma_launch_args.flags */
+#define MA_FLAG_FA_ONLY 1u    /* run the attention stage only (fills O_scratch)         */
+
+typedef struct ma_devinfo {
+  int32_t cc_major, cc_minor, num_sms, max_smem_optin;
+  int32_t kernel_threads, kernel_smem_bytes, kernel_regs, max_ctas; /* of the fused kernel */
+} ma_devinfo;
+
+/*
+ * Everything FusedFaOprojArWorkspace.create() + compile() fix for the lifetime of a
+ * workspace (src/mega_attention/runtime/workspace.py:46-150, :174-194).  Buffer shapes
+ * and dtypes are the reference's (workspace.py:116-139):
+ *   Q [max_tot_q, H_local, D] bf16      K, V [max_tot_k, H_kv, D] bf16
+ *   W_o [K_local, hidden_pad] bf16 (columns >= hidden zero)
+ *   o_scratch [max_row_tiles, 128, H_local, D] bf16
+ *   csym [max_row_tiles, 128, num_out, 128] bf16 (symmetric across ranks when tp > 1)
+ *   ctrl u32[8]  sync_ctrl u32[3]  actv i32[6]  head_ready u32[max_row_tiles]
+ *   oproj_queue u32[max_total_oproj]  ready_count u32[max_owner_slots] (symmetric)
+ *   ready_bits u64[max_owner_words] (symmetric)  ar_done_bits u64[max_owner_words]
+ *   nvl_signal i32[2] (symmetric)  cu_q, cu_k i32[max_batch+1]  fa_b, fa_mb i32[max_row_tiles]
+ *   status u32[8]
+ * All control buffers must be zero when the plan is first launched.
+ */
+typedef struct ma_plan_desc {
+  int32_t device;
+  int32_t tp_size, rank;
+  int32_t H_local, H_kv, D, hidden;
+  int32_t super_group_n_tiles;
+  int32_t max_row_tiles, max_batch, max_tot_q, max_tot_k;
+  float softmax_scale;            /* <= 0: D^-0.5                                       */
+  uint32_t wait_limit_ms;         /* bound of every device-side wait; 0: default 2000   */
+  uint64_t Q, K, V, W_o, o_scratch, csym;
+  uint64_t ctrl, sync_ctrl, actv, head_ready, oproj_queue;
+  uint64_t ready_count, ready_bits, ar_done_bits, nvl_signal;
+  uint64_t cu_q, cu_k, fa_b, fa_mb, status;
+  uint64_t csym_multicast;                      /* NVLS multicast address of csym; 0 if tp==1 */
+  uint64_t peer_ready_count[MA_MAX_TP];         /* per-rank addresses of the symmetric buffers */
+  uint64_t peer_ready_bits[MA_MAX_TP];
+  uint64_t peer_nvl_signal[MA_MAX_TP];
+} ma_plan_desc;
+
+/* Role weights etc.: the arguments of FusedFaOprojArWorkspace.compile()
+ * (workspace.py:174-175) that the reference bakes at JIT time and this library takes per
+ * launch. */
+typedef struct ma_launch_args {
+  int32_t w_fa, w_oproj, w_ar;
+  int32_t num_ctas;               /* <= 0: one per SM                                    */
+  uint32_t flags;
+} ma_launch_args;
+
+typedef struct ma_status {
+  uint32_t code;                  /* 0 = clean; else which wait gave up                  */
+  uint32_t site, cta, aux;
+} ma_status;
+
+typedef struct ma_plan ma_plan;
+
+/* Device / kernel facts (no reference counterpart; the reference hard-codes 132 CTAs,
+ * benchmarks/bench_fused_fa_oproj_ar.py:217). */
+int ma_query_device(int device, ma_devinfo* out);
+
+/* Stands in for FusedFaOprojArWorkspace.compile() -> cute.compile(...)
+ * (workspace.py:174-194): encodes the TMA descriptors over the capacity-shaped buffers. */
+int ma_plan_create(const ma_plan_desc* desc, ma_plan** out);
+
+/* Stands in for FusedFaOprojArWorkspace.launch() (workspace.py:237-240).  Asynchronous on
+ * `stream`; one launch in flight per plan.  With tp > 1 every rank must launch the same
+ * layer: the kernel ends with a cross-rank barrier. */
+int ma_launch(ma_plan* plan, const ma_launch_args* args, void* stream);
+
+/* Reads the device status block (synchronises `stream` first).  No reference
+ * counterpart: the reference's device waits are unbounded. */
+int ma_read_status(ma_plan* plan, void* stream, ma_status* out);
+
+void ma_plan_destroy(ma_plan* plan);
+
+const char* ma_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MEGAATTN_B200_H_ */

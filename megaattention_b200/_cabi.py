@@ -1,0 +1,95 @@
+"""ctypes binding of ``include/megaattn_b200.h``.
+
+There is no fallback: if the shared library is missing (and cannot be built) or a symbol
+is absent, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+MA_MAX_TP = 8
+MA_FLAG_FA_ONLY = 1
+
+MA_OK = 0
+MA_ERR_INVALID = -1
+MA_ERR_CUDA = -2
+MA_ERR_NOT_SM100 = -3
+MA_ERR_DEVICE_TIMEOUT = -4
+MA_ERR_CAPACITY = -5
+
+EXPORTS = ("ma_query_device", "ma_plan_create", "ma_launch", "ma_read_status",
+           "ma_plan_destroy", "ma_strerror")
+
+
+class DevInfo(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "cc_major", "cc_minor", "num_sms", "max_smem_optin",
+        "kernel_threads", "kernel_smem_bytes", "kernel_regs", "max_ctas")]
+
+
+class PlanDesc(C.Structure):
+    _fields_ = (
+        [(n, C.c_int32) for n in (
+            "device", "tp_size", "rank", "H_local", "H_kv", "D", "hidden",
+            "super_group_n_tiles", "max_row_tiles", "max_batch", "max_tot_q", "max_tot_k")]
+        + [("softmax_scale", C.c_float), ("wait_limit_ms", C.c_uint32)]
+        + [(n, C.c_uint64) for n in (
+            "Q", "K", "V", "W_o", "o_scratch", "csym",
+            "ctrl", "sync_ctrl", "actv", "head_ready", "oproj_queue",
+            "ready_count", "ready_bits", "ar_done_bits", "nvl_signal",
+            "cu_q", "cu_k", "fa_b", "fa_mb", "status", "csym_multicast")]
+        + [("peer_ready_count", C.c_uint64 * MA_MAX_TP),
+           ("peer_ready_bits", C.c_uint64 * MA_MAX_TP),
+           ("peer_nvl_signal", C.c_uint64 * MA_MAX_TP)]
+    )
+
+
+class LaunchArgs(C.Structure):
+    _fields_ = [("w_fa", C.c_int32), ("w_oproj", C.c_int32), ("w_ar", C.c_int32),
+                ("num_ctas", C.c_int32), ("flags", C.c_uint32)]
+
+
+class Status(C.Structure):
+    _fields_ = [("code", C.c_uint32), ("site", C.c_uint32), ("cta", C.c_uint32),
+                ("aux", C.c_uint32)]
+
+
+def _load():
+    path = _build.LIB
+    if not os.path.exists(path) or _build._stale():
+        try:
+            _build.build()
+        except Exception as exc:  # no nvcc on this machine: use what is there, if anything
+            if not os.path.exists(path):
+                raise ImportError(f"libmegaattn_b200.so is missing and cannot be built: {exc}")
+    lib = C.CDLL(path)
+    for name in EXPORTS:
+        getattr(lib, name)     # AttributeError if the library does not export it
+    lib.ma_query_device.argtypes = [C.c_int, C.POINTER(DevInfo)]
+    lib.ma_query_device.restype = C.c_int
+    lib.ma_plan_create.argtypes = [C.POINTER(PlanDesc), C.POINTER(C.c_void_p)]
+    lib.ma_plan_create.restype = C.c_int
+    lib.ma_launch.argtypes = [C.c_void_p, C.POINTER(LaunchArgs), C.c_void_p]
+    lib.ma_launch.restype = C.c_int
+    lib.ma_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(Status)]
+    lib.ma_read_status.restype = C.c_int
+    lib.ma_plan_destroy.argtypes = [C.c_void_p]
+    lib.ma_plan_destroy.restype = None
+    lib.ma_strerror.argtypes = [C.c_int]
+    lib.ma_strerror.restype = C.c_char_p
+    return lib
+
+
+lib = _load()
+
+
+def strerror(code: int) -> str:
+    return lib.ma_strerror(int(code)).decode()
+
+
+def check(code: int, what: str):
+    if code != MA_OK:
+        raise RuntimeError(f"{what}: {strerror(code)} ({code})")

@@ -1,0 +1,242 @@
+// C ABI (include/megaattn_b200.h): plan creation (TMA descriptor encoding), launch,
+// status read-back.  Host code only; the kernel lives in fused_prefill.cu.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <new>
+
+#include "../../include/megaattn_b200.h"
+#include "kparams.h"
+
+namespace ma {
+cudaError_t launch_fused_prefill(const CUtensorMap* maps, const KParams& kp, int num_ctas,
+                                 cudaStream_t stream);
+cudaError_t fused_prefill_attributes(cudaFuncAttributes* out);
+}  // namespace ma
+
+struct ma_plan {
+  ma::KParams kp;
+  CUtensorMap maps[5];   // Q, K, V, O_scratch (2-D), W_o
+  int device;
+  int num_sms;
+};
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) !=
+          cudaSuccess || qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  return fn;
+}
+
+// bf16 tensor, innermost dimension contiguous, 128-byte swizzle, zero fill out of bounds
+int encode(CUtensorMap* out, uint64_t base, int rank, const uint64_t* dims,
+           const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeTiledFn enc = get_encoder();
+  if (!enc) return MA_ERR_CUDA;
+  if (base == 0 || (base & 15u)) return MA_ERR_INVALID;
+  cuuint64_t d[3], s[2];
+  cuuint32_t b[3], e[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) {
+    if (strides_bytes[i] & 15u) return MA_ERR_INVALID;
+    s[i] = strides_bytes[i];
+  }
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+                   reinterpret_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MA_OK : MA_ERR_CUDA;
+}
+
+int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace
+
+extern "C" {
+
+const char* ma_strerror(int code) {
+  switch (code) {
+    case MA_OK: return "ok";
+    case MA_ERR_INVALID: return "invalid argument or unsupported shape";
+    case MA_ERR_CUDA: return "CUDA call failed";
+    case MA_ERR_NOT_SM100: return "device is not compute capability 10.x";
+    case MA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case MA_ERR_CAPACITY: return "request exceeds a stated maximum";
+    default: return "unknown error";
+  }
+}
+
+int ma_query_device(int device, ma_devinfo* out) {
+  if (!out) return MA_ERR_INVALID;
+  memset(out, 0, sizeof(*out));
+  int v = 0;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess)
+    return MA_ERR_CUDA;
+  out->cc_major = v;
+  cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMinor, device); out->cc_minor = v;
+  cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device); out->num_sms = v;
+  cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+  out->max_smem_optin = v;
+  out->kernel_threads = ma::kThreads;
+  out->kernel_smem_bytes = ma::kSmemDynamic;
+  out->max_ctas = out->num_sms;   // 1 CTA per SM: the kernel takes > half of shared memory
+  if (out->cc_major != 10) return MA_ERR_NOT_SM100;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaSetDevice(device);
+  cudaFuncAttributes fa;
+  cudaError_t e = ma::fused_prefill_attributes(&fa);
+  cudaSetDevice(cur);
+  if (e != cudaSuccess) return MA_ERR_CUDA;
+  out->kernel_regs = fa.numRegs;
+  return MA_OK;
+}
+
+int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
+  if (!d || !out) return MA_ERR_INVALID;
+  *out = nullptr;
+  if (d->D != 128) return MA_ERR_INVALID;                      // head_dim 128 only
+  if (d->tp_size < 1 || d->tp_size > MA_MAX_TP || d->rank < 0 || d->rank >= d->tp_size)
+    return MA_ERR_INVALID;
+  if (d->H_local < 1 || d->H_kv < 1 || d->H_local % d->H_kv) return MA_ERR_INVALID;
+  if (d->super_group_n_tiles < 1 || d->super_group_n_tiles > 4) return MA_ERR_INVALID;
+  if (d->hidden < 1 || d->max_row_tiles < 1 || d->max_batch < 1) return MA_ERR_INVALID;
+  if (d->max_tot_q < 1 || d->max_tot_k < 1) return MA_ERR_INVALID;
+  const uint64_t need[] = {d->Q, d->K, d->V, d->W_o, d->o_scratch, d->csym, d->ctrl, d->sync_ctrl,
+                           d->actv, d->head_ready, d->oproj_queue, d->ready_count, d->ready_bits,
+                           d->ar_done_bits, d->nvl_signal, d->cu_q, d->cu_k, d->fa_b, d->fa_mb,
+                           d->status};
+  for (uint64_t a : need) if (a == 0) return MA_ERR_INVALID;
+  if (d->tp_size > 1) {
+    if (d->csym_multicast == 0) return MA_ERR_INVALID;
+    for (int r = 0; r < d->tp_size; ++r)
+      if (!d->peer_ready_count[r] || !d->peer_ready_bits[r] || !d->peer_nvl_signal[r])
+        return MA_ERR_INVALID;
+  }
+
+  int cc = 0, sms = 0;
+  if (cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, d->device) != cudaSuccess)
+    return MA_ERR_CUDA;
+  if (cc != 10) return MA_ERR_NOT_SM100;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
+
+  ma_plan* pl = new (std::nothrow) ma_plan;
+  if (!pl) return MA_ERR_CUDA;
+  memset(pl, 0, sizeof(*pl));
+  pl->device = d->device;
+  pl->num_sms = sms;
+
+  ma::KParams& k = pl->kp;
+  k.H = d->H_local; k.Hkv = d->H_kv; k.q_per_kv = d->H_local / d->H_kv;
+  k.K_local = d->H_local * 128; k.hidden = d->hidden;
+  k.num_out = cdiv(d->hidden, 128);
+  k.sg = d->super_group_n_tiles < k.num_out ? d->super_group_n_tiles : k.num_out;
+  k.sg = d->super_group_n_tiles;
+  k.nsg = cdiv(k.num_out, k.sg);
+  k.tp = d->tp_size; k.rank = d->rank;
+  const float scale = d->softmax_scale > 0.f ? d->softmax_scale : 0.08838834764831845f;
+  k.scale_log2 = scale * 1.4426950408889634f;
+  k.pair = (k.q_per_kv % 2 == 0) ? 1 : 0;
+  k.max_row_tiles = d->max_row_tiles;
+  const long long max_total = static_cast<long long>(d->max_row_tiles) * k.nsg;
+  k.max_owner_slots = static_cast<int>((max_total + d->tp_size - 1) / d->tp_size);
+  k.max_owner_words = cdiv(k.max_owner_slots, 64);
+  k.wait_limit_ns = 1000000ull * (d->wait_limit_ms ? d->wait_limit_ms : 2000u);
+  k.o_scratch = reinterpret_cast<uint16_t*>(d->o_scratch);
+  k.csym = reinterpret_cast<uint16_t*>(d->csym);
+  k.ctrl = reinterpret_cast<uint32_t*>(d->ctrl);
+  k.sync_ctrl = reinterpret_cast<uint32_t*>(d->sync_ctrl);
+  k.actv = reinterpret_cast<const int*>(d->actv);
+  k.head_ready = reinterpret_cast<uint32_t*>(d->head_ready);
+  k.oproj_queue = reinterpret_cast<uint32_t*>(d->oproj_queue);
+  k.ready_count = reinterpret_cast<uint32_t*>(d->ready_count);
+  k.ready_bits = reinterpret_cast<unsigned long long*>(d->ready_bits);
+  k.ar_done_bits = reinterpret_cast<unsigned long long*>(d->ar_done_bits);
+  k.nvl_signal = reinterpret_cast<int*>(d->nvl_signal);
+  k.cu_q = reinterpret_cast<const int*>(d->cu_q);
+  k.cu_k = reinterpret_cast<const int*>(d->cu_k);
+  k.fa_b = reinterpret_cast<const int*>(d->fa_b);
+  k.fa_mb = reinterpret_cast<const int*>(d->fa_mb);
+  k.status = reinterpret_cast<uint32_t*>(d->status);
+  k.csym_mc = d->csym_multicast;
+  for (int r = 0; r < MA_MAX_TP; ++r) {
+    k.peer_rc[r] = d->peer_ready_count[r];
+    k.peer_rb[r] = d->peer_ready_bits[r];
+    k.peer_nvl[r] = d->peer_nvl_signal[r];
+  }
+
+  const uint64_t H = d->H_local, Hkv = d->H_kv, KL = k.K_local;
+  const uint64_t hidden_pad = static_cast<uint64_t>(k.num_out) * 128;
+  int rc = MA_OK;
+  {
+    const uint64_t dims[3] = {128, H, static_cast<uint64_t>(d->max_tot_q)};
+    const uint64_t str[2] = {256, H * 256};
+    const uint32_t box[3] = {64, 1, 128};
+    rc = encode(&pl->maps[0], d->Q, 3, dims, str, box);
+  }
+  if (rc == MA_OK) {
+    const uint64_t dims[3] = {128, Hkv, static_cast<uint64_t>(d->max_tot_k)};
+    const uint64_t str[2] = {256, Hkv * 256};
+    const uint32_t box[3] = {64, 1, 128};
+    rc = encode(&pl->maps[1], d->K, 3, dims, str, box);
+    if (rc == MA_OK) rc = encode(&pl->maps[2], d->V, 3, dims, str, box);
+  }
+  if (rc == MA_OK) {
+    const uint64_t dims[2] = {KL, static_cast<uint64_t>(d->max_row_tiles) * 128};
+    const uint64_t str[1] = {KL * 2};
+    const uint32_t box[2] = {64, 128};
+    rc = encode(&pl->maps[3], d->o_scratch, 2, dims, str, box);
+  }
+  if (rc == MA_OK) {
+    const uint64_t dims[2] = {hidden_pad, KL};
+    const uint64_t str[1] = {hidden_pad * 2};
+    const uint32_t box[2] = {64, 64};
+    rc = encode(&pl->maps[4], d->W_o, 2, dims, str, box);
+  }
+  if (rc != MA_OK) { delete pl; return rc; }
+  *out = pl;
+  return MA_OK;
+}
+
+int ma_launch(ma_plan* pl, const ma_launch_args* a, void* stream) {
+  if (!pl || !a) return MA_ERR_INVALID;
+  ma::KParams kp = pl->kp;
+  kp.w_fa = a->w_fa; kp.w_oproj = a->w_oproj;
+  kp.w_ar = (kp.tp > 1) ? a->w_ar : 0;          // one rank: no AllReduce role
+  kp.flags = a->flags;
+  if (kp.w_fa < 0 || kp.w_oproj < 0 || kp.w_ar < 0 || kp.w_fa + kp.w_oproj + kp.w_ar < 1)
+    return MA_ERR_INVALID;
+  int n = a->num_ctas > 0 ? a->num_ctas : pl->num_sms;
+  if (n > pl->num_sms) n = pl->num_sms;          // grid barrier needs every CTA resident
+  cudaError_t e = ma::launch_fused_prefill(pl->maps, kp, n, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MA_OK : MA_ERR_CUDA;
+}
+
+int ma_read_status(ma_plan* pl, void* stream, ma_status* out) {
+  if (!pl || !out) return MA_ERR_INVALID;
+  uint32_t h[4] = {0, 0, 0, 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(h, pl->kp.status, sizeof(h), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return MA_ERR_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return MA_ERR_CUDA;
+  out->code = h[0]; out->site = h[1]; out->cta = h[2]; out->aux = h[3];
+  return h[0] == 0 ? MA_OK : MA_ERR_DEVICE_TIMEOUT;
+}
+
+void ma_plan_destroy(ma_plan* pl) { delete pl; }
+
+}  // extern "C"

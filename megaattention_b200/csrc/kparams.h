@@ -1,0 +1,60 @@
+// Kernel parameter block shared by the host launcher and the device code.
+#pragma once
+#include <stdint.h>
+
+namespace ma {
+
+// Control-word indices: same numbering as the reference kernel
+// (src/mega_attention/kernels/sm90/fused_fa_oproj_ar.py:47-67), which host code reads.
+enum : int {
+  C_FA_COUNTER = 0, C_FA_DONE = 1, C_OP_RESERVE = 2, C_OP_PUBLISH = 3,
+  C_OP_CONSUME = 4, C_OP_DONE = 5, C_AR_DONE = 6, C_AR_CURSOR = 7
+};
+enum : int { S_GS_QUIESCE = 0, S_GS_CLEANDONE = 1, S_NVL_COUNTER = 2 };
+enum : int { MODE_IDLE = 0, MODE_FA = 1, MODE_OPROJ = 2, MODE_AR = 3, MODE_DONE = 4 };
+
+// status[0] codes
+enum : uint32_t {
+  ST_OK = 0, ST_TIMEOUT_MBAR = 1, ST_TIMEOUT_PUBLISH = 2, ST_TIMEOUT_GRID = 3,
+  ST_TIMEOUT_NVL = 4, ST_BAD_DESC = 5
+};
+
+constexpr int kMaxTp = 8;
+
+struct KParams {
+  int H, Hkv, q_per_kv, K_local, hidden, num_out, sg, nsg;
+  int tp, rank;
+  int w_fa, w_oproj, w_ar;
+  uint32_t flags;
+  float scale_log2;
+  int pair;                       // 1: claim two q heads (same kv head) per FA task
+  int max_row_tiles, max_owner_slots, max_owner_words;
+  unsigned long long wait_limit_ns;
+
+  uint16_t* o_scratch;            // bf16 bits
+  uint16_t* csym;
+  uint32_t* ctrl;
+  uint32_t* sync_ctrl;
+  const int* actv;
+  uint32_t* head_ready;
+  uint32_t* oproj_queue;
+  uint32_t* ready_count;
+  unsigned long long* ready_bits;
+  unsigned long long* ar_done_bits;
+  int* nvl_signal;
+  const int* cu_q;
+  const int* cu_k;
+  const int* fa_b;
+  const int* fa_mb;
+  uint32_t* status;
+
+  unsigned long long csym_mc;
+  unsigned long long peer_rc[kMaxTp];
+  unsigned long long peer_rb[kMaxTp];
+  unsigned long long peer_nvl[kMaxTp];
+};
+
+constexpr int kThreads = 384;
+constexpr int kSmemDynamic = 65536 + 4 * 32768 + 1024;   // Q x2, K/V ring x4, align slack
+
+}  // namespace ma

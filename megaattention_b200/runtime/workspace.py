@@ -1,0 +1,279 @@
+"""Long-lived workspace of the fused FlashAttention -> O_proj -> AllReduce kernel.
+
+Same surface as the reference's ``FusedFaOprojArWorkspace``
+(``src/mega_attention/runtime/workspace.py``): ``create`` (:46-150) allocates every buffer
+once at a bucket capacity and, with ``tp_size > 1``, rendezvous-es the symmetric ones;
+``compile`` (:174-194) fixes the launch configuration; ``set_layer`` (:197-235) fills the
+active prefixes and the six active counts; ``launch`` (:237-240) runs one layer with no
+host-side reset in between; ``debug_zero_all`` (:243-248) is for fault localisation only.
+
+Differences a caller can observe:
+
+* nothing is JIT-compiled: ``compile`` builds a plan through the C ABI
+  (``ma_plan_create``) and the role weights / CTA count are launch arguments;
+* ``set_layer`` validates *every* capacity before copying anything;
+* device-side waits are bounded: ``check_status`` raises ``RuntimeError`` when one gave up;
+* ``paged=True`` is not available.
+
+torch is used for device memory, streams and (tp > 1) symmetric-memory bootstrap only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from .. import _cabi
+from ..metadata.row_desc import active_counts, oproj_task_counts
+
+NUM_CTRL = 8
+NUM_SYNC = 3
+NUM_STATUS = 8
+
+
+class FusedFaOprojArWorkspace:
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+        self._plan = None
+        self._args = None
+        self._meta = None
+
+    # ------------------------------------------------------------------ create
+    @classmethod
+    def create(cls, group_name, max_num_row_tiles, hidden, H_local, D,
+               tp_size=1, rank=0, N_TILE=128, super_group_n_tiles=4, q_per_kv=1,
+               max_num_batch=None, max_tot_k=None, dtype=torch.bfloat16, device=None,
+               paged=False, page_size=128, max_num_pages=None,
+               max_num_pages_per_seq=None):
+        assert not paged, "paged KV is not available in this build"
+        assert dtype == torch.bfloat16 and D == 128 and N_TILE == 128
+        assert H_local % q_per_kv == 0
+        assert 1 <= super_group_n_tiles <= 4, "a super-group is at most 512 TMEM columns"
+        dev = torch.device(device if device is not None
+                           else f"cuda:{torch.cuda.current_device()}")
+        H_kv = H_local // q_per_kv
+        K_local = H_local * D
+        if max_num_batch is None:
+            max_num_batch = max_num_row_tiles
+        num_out, nsg, max_total = oproj_task_counts(
+            max_num_row_tiles, hidden, N_TILE, super_group_n_tiles)
+        hidden_pad = num_out * N_TILE
+        tot_cap = max_num_row_tiles * 128
+        if max_tot_k is None:
+            max_tot_k = tot_cap
+        max_owner_slots = (max_total + tp_size - 1) // tp_size
+        max_owner_words = (max_owner_slots + 63) // 64
+
+        def zeros(shape, dt):
+            return torch.zeros(shape, dtype=dt, device=dev)
+
+        handles = None
+        if tp_size > 1:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+
+            def sym(shape, dt):
+                t = symm_mem.empty(*shape, device=dev, dtype=dt)
+                t.zero_()
+                return t, symm_mem.rendezvous(t, group_name)
+
+            csym, hC = sym((max_num_row_tiles, 128, num_out, N_TILE), dtype)
+            assert hC.has_multicast_support, "NVLS multicast is required for tp_size > 1"
+            rco, hRC = sym((max_owner_slots,), torch.uint32)
+            rbits, hRB = sym((max_owner_words,), torch.int64)
+            nvl, hN = sym((2,), torch.int32)
+            csym_mc_ptr = int(hC.multicast_ptr)
+            rc_ptrs = [int(hRC.buffer_ptrs[r]) for r in range(tp_size)]
+            rb_ptrs = [int(hRB.buffer_ptrs[r]) for r in range(tp_size)]
+            nvl_peer_ptrs = [int(hN.buffer_ptrs[r]) for r in range(tp_size)]
+            handles = (hC, hRC, hRB, hN)
+        else:
+            csym = zeros((max_num_row_tiles, 128, num_out, N_TILE), dtype)
+            rco = zeros(max_owner_slots, torch.uint32)
+            rbits = zeros(max_owner_words, torch.int64)
+            nvl = zeros(2, torch.int32)
+            csym_mc_ptr = 0
+            rc_ptrs, rb_ptrs, nvl_peer_ptrs = [], [], []
+
+        ws = cls(
+            dev=dev, dtype=dtype, tp_size=tp_size, rank=rank, group_name=group_name,
+            H_local=H_local, H_kv=H_kv, D=D, K_local=K_local, hidden=hidden,
+            hidden_pad=hidden_pad, N_TILE=N_TILE, super_group_n_tiles=super_group_n_tiles,
+            q_per_kv=q_per_kv, num_out=num_out, num_super_groups=nsg,
+            max_num_row_tiles=max_num_row_tiles, max_num_batch=max_num_batch,
+            max_total_oproj=max_total, tot_cap=tot_cap, max_tot_k=max_tot_k,
+            paged=False, page_size=page_size,
+            ctrl=zeros(NUM_CTRL, torch.uint32), sync_ctrl=zeros(NUM_SYNC, torch.uint32),
+            actv=zeros(6, torch.int32), status=zeros(NUM_STATUS, torch.uint32),
+            head_ready=zeros(max_num_row_tiles, torch.uint32),
+            oproj_queue=zeros(max_total, torch.uint32),
+            ar_done_bits=zeros(max_owner_words, torch.int64),
+            cu_q=zeros(max_num_batch + 1, torch.int32),
+            cu_k=zeros(max_num_batch + 1, torch.int32),
+            fa_b=zeros(max_num_row_tiles, torch.int32),
+            fa_mb=zeros(max_num_row_tiles, torch.int32),
+            Q=zeros((tot_cap, H_local, D), dtype),
+            K=zeros((max_tot_k, H_kv, D), dtype),
+            V=zeros((max_tot_k, H_kv, D), dtype),
+            W_o=zeros((K_local, hidden_pad), dtype),
+            Oscr=zeros((max_num_row_tiles, 128, H_local, D), dtype),
+            csym=csym, rco=rco, rbits=rbits, nvl=nvl,
+            csym_mc_ptr=csym_mc_ptr, nvl_peer_ptrs=nvl_peer_ptrs,
+            rc_ptrs=rc_ptrs, rb_ptrs=rb_ptrs, _handles=handles,
+        )
+        # The first launch relies on every control word being zero on every rank before
+        # any rank issues a remote control write.
+        torch.cuda.synchronize(dev)
+        if tp_size > 1:
+            import torch.distributed as dist
+            if dist.is_initialized():
+                dist.barrier()
+        return ws
+
+    # ------------------------------------------------------------------ compile
+    def compile(self, w_fa=4, w_oproj=1, w_ar=1, num_ctas=None, kv_stages=2,
+                K_CHUNK=64, oproj_stages=4, softmax_scale=None, wait_limit_ms=0):
+        """Fix the launch configuration and build the C-ABI plan.
+
+        ``kv_stages``, ``K_CHUNK`` and ``oproj_stages`` are accepted for signature
+        compatibility; the staging depths of the sm_100a kernel are fixed.
+        ``num_ctas=None`` means one CTA per SM.
+        """
+        if self._plan is not None:
+            _cabi.lib.ma_plan_destroy(self._plan)
+            self._plan = None
+        d = _cabi.PlanDesc()
+        d.device = self.dev.index if self.dev.index is not None else torch.cuda.current_device()
+        d.tp_size, d.rank = self.tp_size, self.rank
+        d.H_local, d.H_kv, d.D, d.hidden = self.H_local, self.H_kv, self.D, self.hidden
+        d.super_group_n_tiles = self.super_group_n_tiles
+        d.max_row_tiles, d.max_batch = self.max_num_row_tiles, self.max_num_batch
+        d.max_tot_q, d.max_tot_k = self.tot_cap, self.max_tot_k
+        d.softmax_scale = float(softmax_scale) if softmax_scale is not None else 0.0
+        d.wait_limit_ms = int(wait_limit_ms)
+        for name, t in (("Q", self.Q), ("K", self.K), ("V", self.V), ("W_o", self.W_o),
+                        ("o_scratch", self.Oscr), ("csym", self.csym), ("ctrl", self.ctrl),
+                        ("sync_ctrl", self.sync_ctrl), ("actv", self.actv),
+                        ("head_ready", self.head_ready), ("oproj_queue", self.oproj_queue),
+                        ("ready_count", self.rco), ("ready_bits", self.rbits),
+                        ("ar_done_bits", self.ar_done_bits), ("nvl_signal", self.nvl),
+                        ("cu_q", self.cu_q), ("cu_k", self.cu_k), ("fa_b", self.fa_b),
+                        ("fa_mb", self.fa_mb), ("status", self.status)):
+            setattr(d, name, t.data_ptr())
+        d.csym_multicast = self.csym_mc_ptr
+        for r in range(self.tp_size if self.tp_size > 1 else 0):
+            d.peer_ready_count[r] = self.rc_ptrs[r]
+            d.peer_ready_bits[r] = self.rb_ptrs[r]
+            d.peer_nvl_signal[r] = self.nvl_peer_ptrs[r]
+        plan = C.c_void_p()
+        _cabi.check(_cabi.lib.ma_plan_create(C.byref(d), C.byref(plan)), "ma_plan_create")
+        self._plan = plan
+        self._args = _cabi.LaunchArgs(int(w_fa), int(w_oproj), int(w_ar),
+                                      int(num_ctas) if num_ctas else 0, 0)
+        self._ts = torch.cuda.current_stream(self.dev)
+        return self
+
+    # ------------------------------------------------------------------ per layer
+    def set_layer(self, meta, Q, K, V, W_o, page_table=None, cache_seqlens=None):
+        """Copy one layer's inputs and varlen metadata into the active prefixes.
+
+        ``Q [tot_q,H_local,D]``, ``K/V [tot_k,H_kv,D]``, ``W_o [K_local,hidden]``; host
+        (pinned) or device tensors.  Raises ``AssertionError`` on any capacity violation
+        before touching the workspace.
+        """
+        assert page_table is None and cache_seqlens is None, "paged KV is not available"
+        R, nb = meta.num_row_tiles, meta.num_batch
+        tq, tk = Q.shape[0], K.shape[0]
+        assert R <= self.max_num_row_tiles and nb <= self.max_num_batch
+        assert tq <= self.tot_cap
+        assert tk <= self.max_tot_k and V.shape[0] == tk
+        assert tuple(Q.shape[1:]) == (self.H_local, self.D)
+        assert tuple(K.shape[1:]) == (self.H_kv, self.D) == tuple(V.shape[1:])
+        assert tuple(W_o.shape) == (self.K_local, self.hidden)
+        assert int(meta.cu_seqlens_q[-1]) == tq and int(meta.cu_seqlens_k[-1]) == tk
+        with torch.cuda.stream(self._stream()):
+            self.Q[:tq].copy_(Q, non_blocking=True)
+            self.W_o[:, :self.hidden].copy_(W_o, non_blocking=True)
+            self.K[:tk].copy_(K, non_blocking=True)
+            self.V[:tk].copy_(V, non_blocking=True)
+            self._set_meta(meta)
+
+    def set_meta(self, meta):
+        """Metadata only (inputs already resident in ``self.Q/K/V/W_o``)."""
+        assert meta.num_row_tiles <= self.max_num_row_tiles
+        assert meta.num_batch <= self.max_num_batch
+        assert int(meta.cu_seqlens_q[-1]) <= self.tot_cap
+        assert int(meta.cu_seqlens_k[-1]) <= self.max_tot_k
+        with torch.cuda.stream(self._stream()):
+            self._set_meta(meta)
+
+    def _set_meta(self, meta):
+        R, nb = meta.num_row_tiles, meta.num_batch
+        # one small H2D copy: cu_q | cu_k | fa_b | fa_mb | actv packed on the host
+        host = np.concatenate([
+            np.asarray(meta.cu_seqlens_q, dtype=np.int32),
+            np.asarray(meta.cu_seqlens_k, dtype=np.int32),
+            np.asarray(meta.batch_idx, dtype=np.int32),
+            np.asarray(meta.m_block, dtype=np.int32),
+            active_counts(R, self.H_local, self.num_super_groups, self.tp_size, self.rank),
+        ])
+        stage = torch.from_numpy(host).to(self.dev, non_blocking=False)
+        o = 0
+        for dst, n in ((self.cu_q, nb + 1), (self.cu_k, nb + 1), (self.fa_b, R),
+                       (self.fa_mb, R), (self.actv, 6)):
+            dst[:n].copy_(stage[o:o + n])
+            o += n
+        self._meta = meta
+
+    def _stream(self):
+        return getattr(self, "_ts", None) or torch.cuda.current_stream(self.dev)
+
+    def launch(self, flags=0):
+        assert self._plan is not None, "call compile() first"
+        args = _cabi.LaunchArgs(self._args.w_fa, self._args.w_oproj, self._args.w_ar,
+                                self._args.num_ctas, int(flags))
+        _cabi.check(_cabi.lib.ma_launch(self._plan, C.byref(args),
+                                        C.c_void_p(self._ts.cuda_stream)), "ma_launch")
+
+    def launch_fa_only(self):
+        """Attention stage alone (fills ``Oscr``); used by the unfused baseline."""
+        self.launch(flags=_cabi.MA_FLAG_FA_ONLY)
+
+    def check_status(self):
+        """Synchronise the launch stream and raise if a device-side wait gave up."""
+        st = _cabi.Status()
+        rc = _cabi.lib.ma_read_status(self._plan, C.c_void_p(self._ts.cuda_stream), C.byref(st))
+        if rc != _cabi.MA_OK:
+            raise RuntimeError(
+                f"fused prefill kernel: {_cabi.strerror(rc)} "
+                f"(code={st.code} site=0x{st.site:x} cta={st.cta} aux={st.aux}); "
+                "the workspace control state is undefined — call debug_zero_all()")
+
+    def output(self, meta=None):
+        """De-tiled ``[tot_q, hidden]`` copy of the valid region of ``csym``."""
+        meta = meta or self._meta
+        flat = self.csym.view(self.max_num_row_tiles, 128, self.hidden_pad)
+        tot = int(meta.cu_seqlens_q[-1])
+        out = torch.empty(tot, self.hidden, dtype=self.dtype, device=self.dev)
+        for t in range(meta.num_row_tiles):
+            s, vm = meta.q_tile_start(t), meta.valid_m(t)
+            out[s:s + vm] = flat[t, :vm, :self.hidden]
+        return out
+
+    # ------------------------------------------------------------------ debug
+    def debug_zero_all(self):
+        """Fault localisation only; never on the production / bench / test default path.
+        With tp > 1 every rank must call it, followed by a host barrier."""
+        for t in (self.ctrl, self.sync_ctrl, self.actv, self.head_ready, self.oproj_queue,
+                  self.rco, self.rbits, self.ar_done_bits, self.nvl, self.csym, self.Oscr,
+                  self.status):
+            t.zero_()
+
+    def __del__(self):
+        try:
+            if self._plan is not None:
+                _cabi.lib.ma_plan_destroy(self._plan)
+                self._plan = None
+        except Exception:
+            pass
