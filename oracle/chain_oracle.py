@@ -121,3 +121,24 @@ def err_rel(got, ref):
     """``max|got - ref| / max|ref|`` in fp32 (bench_fused_fa_oproj_ar.py:259-270)."""
     g, r = got.float(), ref.float()
     return float((g - r).abs().max() / r.abs().max().clamp_min(1e-30))
+
+
+def bf16_half_ulp(x):
+    """Half a bf16 unit-in-the-last-place at the magnitude of ``x`` (8 significant bits)."""
+    a = x.float().abs().clamp_min(2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(a)) - 8.0)
+
+
+def err_beyond_rounding(got, ref_fp32, extra_half_ulps=0.0):
+    """``max(|got - ref| - r) / max|ref|`` where ``r`` is the rounding a bf16 result
+    necessarily carries: half a bf16 ulp of the reference value (plus
+    ``extra_half_ulps`` more half-ulps when the reference was itself rounded to bf16).
+
+    ``err_rel`` against an fp32 reference cannot go below 2^-9..2^-8 of the maximum for
+    any bf16-valued result, whatever computed it; this is the part of the error the
+    computation itself is answerable for.
+    """
+    g, r = got.float(), ref_fp32.float()
+    slack = bf16_half_ulp(r) * (1.0 + extra_half_ulps)
+    excess = ((g - r).abs() - slack).clamp_min(0.0)
+    return float(excess.max() / r.abs().max().clamp_min(1e-30))

