@@ -129,10 +129,12 @@ def bf16_half_ulp(x):
     return torch.exp2(torch.floor(torch.log2(a)) - 8.0)
 
 
-def err_beyond_rounding(got, ref_fp32, extra_half_ulps=0.0):
+def err_beyond_rounding(got, ref_fp32, extra_half_ulps=0.0, partials=None):
     """``max(|got - ref| - r) / max|ref|`` where ``r`` is the rounding a bf16 result
     necessarily carries: half a bf16 ulp of the reference value (plus
-    ``extra_half_ulps`` more half-ulps when the reference was itself rounded to bf16).
+    ``extra_half_ulps`` more half-ulps when the reference was itself rounded to bf16, plus
+    half a bf16 ulp of every per-rank partial in ``partials``: with tensor parallelism the
+    path stages each rank's partial in bf16 before the in-switch fp32 reduction).
 
     ``err_rel`` against an fp32 reference cannot go below 2^-9..2^-8 of the maximum for
     any bf16-valued result, whatever computed it; this is the part of the error the
@@ -140,5 +142,7 @@ def err_beyond_rounding(got, ref_fp32, extra_half_ulps=0.0):
     """
     g, r = got.float(), ref_fp32.float()
     slack = bf16_half_ulp(r) * (1.0 + extra_half_ulps)
+    for part in (partials or ()):
+        slack = slack + bf16_half_ulp(part)
     excess = ((g - r).abs() - slack).clamp_min(0.0)
     return float(excess.max() / r.abs().max().clamp_min(1e-30))

@@ -1,0 +1,104 @@
+"""Worker of tests/test_fused_multi_gpu.py (one process per GPU, launched by torchrun).
+
+One workspace, built once, runs a sequence of heterogeneous layers back to back with no
+host-side reset (the pattern of the reference's tests/fused/test_fused_production.py:45-61,
+79-123): full capacity -> one tile, long KV -> short KV, repeats; every layer is checked
+against the CPU oracle (sum over ranks of the per-rank partial, one bf16 cast) and for a
+clean exit; two over-capacity layers must raise AssertionError and leave the workspace
+usable (test_fused_production.py:129-146).
+"""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch
+import torch.distributed as dist
+
+from megaattention_b200.metadata import build_row_desc
+from megaattention_b200.runtime import FusedFaOprojArWorkspace
+from oracle.chain_oracle import fa_oracle, oproj_oracle, err_rel, err_beyond_rounding
+
+MAX_RT, H, QPK, HIDDEN, SG = 12, 4, 2, 640, 4
+LAYERS = [
+    ([1536], None), ([100], None), ([300, 200], None), ([256], [1024]), ([256], None),
+    ([128, 128, 128, 128], None), ([700], [700]), ([64, 200, 130], [64, 328, 130]),
+    ([1536], None), ([1], None), ([513], [1200]), ([300, 200], None),
+]
+
+
+def rnd(shape, seed, std=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(torch.bfloat16)
+
+
+def inputs(layer, rank, sq, sk):
+    s = 7000 + layer * 100 + rank * 10
+    hkv = H // QPK
+    return (rnd((sum(sq), H, 128), s), rnd((sum(sk), hkv, 128), s + 1),
+            rnd((sum(sk), hkv, 128), s + 2), rnd((H * 128, HIDDEN), s + 3, (H * 128) ** -0.5))
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device(f"cuda:{int(os.environ['LOCAL_RANK'])}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    import torch.distributed._symmetric_memory as symm_mem
+    group = dist.group.WORLD.group_name
+    symm_mem.enable_symm_mem_for_group(group)
+    torch.set_num_threads(4)
+    ws = FusedFaOprojArWorkspace.create(
+        group, MAX_RT, HIDDEN, H, 128, tp_size=world, rank=rank, super_group_n_tiles=SG,
+        q_per_kv=QPK, max_tot_k=1536, device=dev)
+    ws.compile(w_fa=2, w_oproj=1, w_ar=1, num_ctas=int(os.environ.get("MA_TEST_CTAS", "24")))
+    worst = 0.0
+    for li, (sq, sk) in enumerate(LAYERS):
+        sk = sq if sk is None else sk
+        meta = build_row_desc(sq, seqlens_k=sk)
+        mine = inputs(li, rank, sq, sk)
+        ws.set_layer(meta, *[t.to(dev) for t in mine])
+        ws.launch()
+        ws.check_status()
+        acc, parts = None, []
+        for r in range(world):
+            Q, K, V, W = inputs(li, r, sq, sk)
+            yp = oproj_oracle(fa_oracle(Q, K, V, sq, sk), W)
+            parts.append(yp)
+            acc = yp.clone() if acc is None else acc + yp
+        got = ws.output(meta).cpu()
+        e_comp = err_beyond_rounding(got, acc, partials=parts)
+        e_raw = err_rel(got, acc.to(torch.bfloat16))
+        ctrl = ws.ctrl.cpu().tolist()
+        tol = 8e-3 if sk != sq else 2e-3
+        ok = e_comp <= tol and ctrl == [0] * 8
+        print(f"[rank {rank}] layer {li} {sq}/{sk}: err_comp={e_comp:.3g} err_rel_bf16={e_raw:.3g} "
+              f"ctrl={ctrl} {'OK' if ok else 'FAIL'}", flush=True)
+        assert ok
+        worst = max(worst, e_comp)
+        # every rank must hold the same bytes
+        mine_sum = got.float().sum().to(dev).double()
+        lo, hi = mine_sum.clone(), mine_sum.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        assert float(lo) == float(hi), "ranks disagree on the reduced output"
+    # over-capacity layers: AssertionError before anything is touched, workspace stays usable
+    for sq, sk in (([1537], None), ([256], [1537])):
+        sk2 = sq if sk is None else sk
+        meta = build_row_desc(sq, seqlens_k=sk2)
+        try:
+            ws.set_layer(meta, *[t.to(dev) for t in inputs(99, rank, sq, sk2)])
+            raise SystemExit("over-capacity layer was accepted")
+        except AssertionError:
+            pass
+    sq = [300, 200]
+    meta = build_row_desc(sq)
+    ws.set_layer(meta, *[t.to(dev) for t in inputs(2, rank, sq, sq)])
+    ws.launch(); ws.check_status()
+    dist.barrier()
+    print(f"[rank {rank}] ALL OK worst err_comp={worst:.3g}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
