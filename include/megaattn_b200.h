@@ -112,6 +112,63 @@ int ma_read_status(ma_plan* plan, void* stream, ma_status* out);
 
 void ma_plan_destroy(ma_plan* plan);
 
+/*
+ * One-call fused prefill for callers that must not allocate device memory.
+ * (No counterpart in the reference, whose workspace allocates everything with torch.)
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits - inside a serving engine
+ * that sized its memory pool at start-up, where one more allocation breaks the pool's
+ * accounting or fails outright because the pool already holds every free byte; on a
+ * latency-critical path where an allocation's implicit device synchronisation is not
+ * acceptable; or in a plug-in that is handed buffers but is forbidden to create any.
+ * Such a caller owns its inputs and its output but cannot give the kernel a workspace.
+ *
+ * The attention-output scratch, the scheduler's control words, the O_proj ready queue and
+ * the tile descriptors live in ONE fixed array inside the library
+ * (MA_NOALLOC_SCRATCH_BYTES of device memory per GPU that loads the library, held until
+ * the process exits).  The call itself allocates nothing: it computes the tile
+ * descriptors on the host, copies them and zeroes the control words with stream-ordered
+ * copies into that array, encodes TMA descriptors on the host and launches the same
+ * kernel as ma_launch (single rank, AllReduce = identity).
+ *
+ * Limits (MA_ERR_CAPACITY beyond them): num_batch <= MA_NOALLOC_MAX_BATCH,
+ * row tiles R = sum ceil(q_len/128) <= MA_NOALLOC_MAX_ROW_TILES,
+ * R * num_super_groups <= MA_NOALLOC_MAX_SLOTS, and
+ * R * 128 * H_local * 128 * 2 bytes <= MA_NOALLOC_OSCRATCH_BYTES.
+ * Shapes: head_dim 128; hidden % 8 == 0; W_o is [H_local*128, hidden] row-major with no
+ * padding; `out` is the tile-padded layout [R, 128, ceil(hidden/128), 128] bf16, of which
+ * only rows < valid_m and columns < hidden are written.
+ *
+ * The first call on a device looks up the array's device address; make that first call
+ * outside any stream capture.  Every call uses the same array: it keeps the previous
+ * call's contents (what has to start from zero is cleared by the call), and two calls
+ * that overlap on the GPU - different streams, or different host threads - race on it.
+ * The device must be current.  The call returns once the work is queued on `stream`;
+ * if `status_out` is not NULL it instead waits for the stream and fills it, returning
+ * MA_ERR_DEVICE_TIMEOUT when a device-side wait gave up.
+ */
+#define MA_NOALLOC_OSCRATCH_BYTES (16u << 20)
+#define MA_NOALLOC_CONTROL_BYTES (64u << 10)
+#define MA_NOALLOC_SCRATCH_BYTES (MA_NOALLOC_OSCRATCH_BYTES + MA_NOALLOC_CONTROL_BYTES)
+#define MA_NOALLOC_MAX_BATCH 512
+#define MA_NOALLOC_MAX_ROW_TILES 512
+#define MA_NOALLOC_MAX_SLOTS 4096
+
+typedef struct ma_noalloc_args {
+  int32_t H_local, H_kv, hidden, super_group_n_tiles;
+  int32_t num_batch;
+  int32_t w_fa, w_oproj, num_ctas;      /* role weights; num_ctas <= 0: one per SM        */
+  float softmax_scale;                  /* <= 0: 128^-0.5                                 */
+  uint32_t wait_limit_ms;               /* 0: 2000                                        */
+  const int32_t* seqlens_q;             /* host, [num_batch]                              */
+  const int32_t* seqlens_k;             /* host, [num_batch]; NULL: same as seqlens_q     */
+  uint64_t Q, K, V, W_o;                /* device, bf16                                   */
+  uint64_t out;                         /* device, bf16, tile-padded layout               */
+  ma_status* status_out;                /* host, may be NULL                              */
+} ma_noalloc_args;
+
+int ma_fused_prefill_noalloc(const ma_noalloc_args* args, void* stream);
+
 const char* ma_strerror(int code);
 
 #ifdef __cplusplus

@@ -21,7 +21,12 @@ MA_ERR_DEVICE_TIMEOUT = -4
 MA_ERR_CAPACITY = -5
 
 EXPORTS = ("ma_query_device", "ma_plan_create", "ma_launch", "ma_read_status",
-           "ma_plan_destroy", "ma_strerror")
+           "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc")
+
+MA_NOALLOC_OSCRATCH_BYTES = 16 << 20
+MA_NOALLOC_MAX_BATCH = 512
+MA_NOALLOC_MAX_ROW_TILES = 512
+MA_NOALLOC_MAX_SLOTS = 4096
 
 
 class DevInfo(C.Structure):
@@ -57,6 +62,16 @@ class Status(C.Structure):
                 ("aux", C.c_uint32)]
 
 
+class NoAllocArgs(C.Structure):
+    _fields_ = [("H_local", C.c_int32), ("H_kv", C.c_int32), ("hidden", C.c_int32),
+                ("super_group_n_tiles", C.c_int32), ("num_batch", C.c_int32),
+                ("w_fa", C.c_int32), ("w_oproj", C.c_int32), ("num_ctas", C.c_int32),
+                ("softmax_scale", C.c_float), ("wait_limit_ms", C.c_uint32),
+                ("seqlens_q", C.POINTER(C.c_int32)), ("seqlens_k", C.POINTER(C.c_int32)),
+                ("Q", C.c_uint64), ("K", C.c_uint64), ("V", C.c_uint64), ("W_o", C.c_uint64),
+                ("out", C.c_uint64), ("status_out", C.POINTER(Status))]
+
+
 def _load():
     path = _build.LIB
     if not os.path.exists(path) or _build._stale():
@@ -78,6 +93,8 @@ def _load():
     lib.ma_read_status.restype = C.c_int
     lib.ma_plan_destroy.argtypes = [C.c_void_p]
     lib.ma_plan_destroy.restype = None
+    lib.ma_fused_prefill_noalloc.argtypes = [C.POINTER(NoAllocArgs), C.c_void_p]
+    lib.ma_fused_prefill_noalloc.restype = C.c_int
     lib.ma_strerror.argtypes = [C.c_int]
     lib.ma_strerror.restype = C.c_char_p
     return lib

@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmegaattn_b200.so")
-SOURCES = ["fused_prefill.cu", "cabi.cu"]
+SOURCES = ["fused_prefill.cu", "cabi.cu", "noalloc.cu"]
 HEADERS = ["ptx.cuh", "kparams.h", os.path.join("..", "..", "include", "megaattn_b200.h")]
 
 

@@ -14,6 +14,8 @@ namespace ma {
 cudaError_t launch_fused_prefill(const CUtensorMap* maps, const KParams& kp, int num_ctas,
                                  cudaStream_t stream);
 cudaError_t fused_prefill_attributes(cudaFuncAttributes* out);
+int encode_bf16_map(CUtensorMap* out, uint64_t base, int rank, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box);
 }  // namespace ma
 
 struct ma_plan {
@@ -65,6 +67,11 @@ int encode(CUtensorMap* out, uint64_t base, int rank, const uint64_t* dims,
 int cdiv(int a, int b) { return (a + b - 1) / b; }
 
 }  // namespace
+
+int ma::encode_bf16_map(CUtensorMap* out, uint64_t base, int rank, const uint64_t* dims,
+                        const uint64_t* strides_bytes, const uint32_t* box) {
+  return encode(out, base, rank, dims, strides_bytes, box);
+}
 
 extern "C" {
 
