@@ -172,6 +172,9 @@ def main():
     ap.add_argument("--no-unfused", action="store_true")
     ap.add_argument("--w", type=str, default=None, help="w_fa,w_oproj,w_ar override")
     ap.add_argument("--ctas", type=int, default=0)
+    ap.add_argument("--stage", default="fused", choices=["fused", "fa"],
+                    help="fa: time the attention stage alone (profiling aid)")
+    ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -245,7 +248,7 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    ms_fused = timed(ws.launch, K, W)
+    ms_fused = timed(ws.launch if args.stage == "fused" else ws.launch_fa_only, K, W)
     clocks = sampler.stop() if sampler else None
     ws.check_status()
 
@@ -277,15 +280,15 @@ def main():
         ws.launch()
         host_out.copy_(ws.csym[:meta.num_row_tiles], non_blocking=True)
 
-    for _ in range(2):
+    n_e2e = 0 if args.no_e2e else max(3, min(K, 10))
+    for _ in range(2 if n_e2e else 0):
         e2e_step()
     torch.cuda.synchronize(); barrier()
     t0 = time.perf_counter()
-    n_e2e = max(3, min(K, 10))
     for _ in range(n_e2e):
         e2e_step()
     torch.cuda.synchronize(); barrier()
-    ms_e2e = (time.perf_counter() - t0) * 1e3 / n_e2e
+    ms_e2e = (time.perf_counter() - t0) * 1e3 / max(n_e2e, 1) if n_e2e else float("nan")
     if world > 1:
         t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -331,7 +334,7 @@ def main():
             "warmup": W, "ms_per_step": ms_fused, "higher_is_better": True,
             "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": f"{wl.name} tp{tp}", "seqlens_q": wl.seqlens_q,
+            "config": {"workload": f"{wl.name} tp{tp}" + ("" if args.stage == "fused" else " (attention stage only)"), "seqlens_q": wl.seqlens_q,
                        "kv_mult": wl.kv_mult, "H_local": h, "H_kv": hkv, "hidden": wl.hidden,
                        "role_weights": list(w), "sg": cfg.sg,
                        "l2": "512 MiB buffer written before every timed launch"},

@@ -55,7 +55,7 @@ typedef struct ma_devinfo {
  *   ctrl u32[8]  sync_ctrl u32[3]  actv i32[6]  head_ready u32[max_row_tiles]
  *   oproj_queue u32[max_total_oproj]  ready_count u32[max_owner_slots] (symmetric)
  *   ready_bits u64[max_owner_words] (symmetric)  ar_done_bits u64[max_owner_words]
- *   nvl_signal i32[2] (symmetric)  cu_q, cu_k i32[max_batch+1]  fa_b, fa_mb i32[max_row_tiles]
+ *   nvl_signal i32[2] (symmetric)  cu_q, cu_k i32[max_batch+1]  fa_b, fa_mb, fa_order i32[max_row_tiles]
  *   status u32[8]
  * All control buffers must be zero when the plan is first launched.
  */
@@ -75,6 +75,9 @@ typedef struct ma_plan_desc {
   uint64_t peer_ready_count[MA_MAX_TP];         /* per-rank addresses of the symmetric buffers */
   uint64_t peer_ready_bits[MA_MAX_TP];
   uint64_t peer_nvl_signal[MA_MAX_TP];
+  uint64_t fa_order;   /* i32[max_row_tiles]: row tiles in the order attention tasks are
+                          claimed (the workspace sorts longest-first); 0 = natural order.
+                          No reference counterpart: the reference claims in tile order. */
 } ma_plan_desc;
 
 /* Role weights etc.: the arguments of FusedFaOprojArWorkspace.compile()
@@ -135,7 +138,7 @@ void ma_plan_destroy(ma_plan* plan);
  * row tiles R = sum ceil(q_len/128) <= MA_NOALLOC_MAX_ROW_TILES,
  * R * num_super_groups <= MA_NOALLOC_MAX_SLOTS, and
  * R * 128 * H_local * 128 * 2 bytes <= MA_NOALLOC_OSCRATCH_BYTES.
- * Shapes: head_dim 128; hidden % 8 == 0; W_o is [H_local*128, hidden] row-major with no
+ * Shapes: head_dim 128; hidden % 64 == 0; W_o is [H_local*128, hidden] row-major with no
  * padding; `out` is the tile-padded layout [R, 128, ceil(hidden/128), 128] bf16, of which
  * only rows < valid_m and columns < hidden are written.
  *

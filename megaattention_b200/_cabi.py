@@ -48,7 +48,8 @@ class PlanDesc(C.Structure):
             "cu_q", "cu_k", "fa_b", "fa_mb", "status", "csym_multicast")]
         + [("peer_ready_count", C.c_uint64 * MA_MAX_TP),
            ("peer_ready_bits", C.c_uint64 * MA_MAX_TP),
-           ("peer_nvl_signal", C.c_uint64 * MA_MAX_TP)]
+           ("peer_nvl_signal", C.c_uint64 * MA_MAX_TP),
+           ("fa_order", C.c_uint64)]
     )
 
 

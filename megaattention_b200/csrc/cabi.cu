@@ -14,8 +14,9 @@ namespace ma {
 cudaError_t launch_fused_prefill(const CUtensorMap* maps, const KParams& kp, int num_ctas,
                                  cudaStream_t stream);
 cudaError_t fused_prefill_attributes(cudaFuncAttributes* out);
-int encode_bf16_map(CUtensorMap* out, uint64_t base, int rank, const uint64_t* dims,
-                    const uint64_t* strides_bytes, const uint32_t* box);
+int encode_path_maps(CUtensorMap* maps, uint64_t Q, uint64_t K, uint64_t V, uint64_t oscr,
+                     uint64_t W, uint64_t H, uint64_t Hkv, uint64_t tot_q, uint64_t tot_k,
+                     uint64_t row_tiles, uint64_t w_width);
 }  // namespace ma
 
 struct ma_plan {
@@ -50,8 +51,8 @@ int encode(CUtensorMap* out, uint64_t base, int rank, const uint64_t* dims,
   EncodeTiledFn enc = get_encoder();
   if (!enc) return MA_ERR_CUDA;
   if (base == 0 || (base & 15u)) return MA_ERR_INVALID;
-  cuuint64_t d[3], s[2];
-  cuuint32_t b[3], e[3] = {1, 1, 1};
+  cuuint64_t d[4], s[3];
+  cuuint32_t b[4], e[4] = {1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }
   for (int i = 0; i + 1 < rank; ++i) {
     if (strides_bytes[i] & 15u) return MA_ERR_INVALID;
@@ -68,9 +69,43 @@ int cdiv(int a, int b) { return (a + b - 1) / b; }
 
 }  // namespace
 
-int ma::encode_bf16_map(CUtensorMap* out, uint64_t base, int rank, const uint64_t* dims,
-                        const uint64_t* strides_bytes, const uint32_t* box) {
-  return encode(out, base, rank, dims, strides_bytes, box);
+// The five TMA descriptors of the path.  A 128 x 128 tile of Q, K or V is fetched by ONE
+// instruction as two 64-wide swizzled panels: the tensor is described as
+// {64 d, tokens, 2 d-halves, heads} so the box {64, 128, 2, 1} lands panel after panel.
+// W_o [K_local, width] is described as {64 n, K_local, width/64 panels}: the box
+// {64, 64, 4} is a 64-k slab of 256 output columns, panel after panel.
+int ma::encode_path_maps(CUtensorMap* maps, uint64_t Q, uint64_t K, uint64_t V, uint64_t oscr,
+                         uint64_t W, uint64_t H, uint64_t Hkv, uint64_t tot_q, uint64_t tot_k,
+                         uint64_t row_tiles, uint64_t w_width) {
+  if (w_width % 64) return MA_ERR_INVALID;
+  const uint64_t KL = H * 128;
+  int rc;
+  {
+    const uint64_t dims[4] = {64, tot_q, 2, H};
+    const uint64_t str[3] = {H * 256, 128, 256};
+    const uint32_t box[4] = {64, 128, 2, 1};
+    rc = encode(&maps[0], Q, 4, dims, str, box);
+  }
+  if (rc == MA_OK) {
+    const uint64_t dims[4] = {64, tot_k, 2, Hkv};
+    const uint64_t str[3] = {Hkv * 256, 128, 256};
+    const uint32_t box[4] = {64, 128, 2, 1};
+    rc = encode(&maps[1], K, 4, dims, str, box);
+    if (rc == MA_OK) rc = encode(&maps[2], V, 4, dims, str, box);
+  }
+  if (rc == MA_OK) {
+    const uint64_t dims[2] = {KL, row_tiles * 128};
+    const uint64_t str[1] = {KL * 2};
+    const uint32_t box[2] = {64, 128};
+    rc = encode(&maps[3], oscr, 2, dims, str, box);
+  }
+  if (rc == MA_OK) {
+    const uint64_t dims[3] = {64, KL, w_width / 64};
+    const uint64_t str[2] = {w_width * 2, 128};
+    const uint32_t box[3] = {64, 64, 4};
+    rc = encode(&maps[4], W, 3, dims, str, box);
+  }
+  return rc;
 }
 
 extern "C" {
@@ -151,7 +186,6 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   k.H = d->H_local; k.Hkv = d->H_kv; k.q_per_kv = d->H_local / d->H_kv;
   k.K_local = d->H_local * 128; k.hidden = d->hidden;
   k.num_out = cdiv(d->hidden, 128);
-  k.sg = d->super_group_n_tiles < k.num_out ? d->super_group_n_tiles : k.num_out;
   k.sg = d->super_group_n_tiles;
   k.nsg = cdiv(k.num_out, k.sg);
   k.tp = d->tp_size; k.rank = d->rank;
@@ -178,6 +212,7 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   k.cu_k = reinterpret_cast<const int*>(d->cu_k);
   k.fa_b = reinterpret_cast<const int*>(d->fa_b);
   k.fa_mb = reinterpret_cast<const int*>(d->fa_mb);
+  k.fa_order = reinterpret_cast<const int*>(d->fa_order);
   k.status = reinterpret_cast<uint32_t*>(d->status);
   k.csym_mc = d->csym_multicast;
   for (int r = 0; r < MA_MAX_TP; ++r) {
@@ -186,34 +221,12 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
     k.peer_nvl[r] = d->peer_nvl_signal[r];
   }
 
-  const uint64_t H = d->H_local, Hkv = d->H_kv, KL = k.K_local;
+  const uint64_t H = d->H_local, Hkv = d->H_kv;
   const uint64_t hidden_pad = static_cast<uint64_t>(k.num_out) * 128;
-  int rc = MA_OK;
-  {
-    const uint64_t dims[3] = {128, H, static_cast<uint64_t>(d->max_tot_q)};
-    const uint64_t str[2] = {256, H * 256};
-    const uint32_t box[3] = {64, 1, 128};
-    rc = encode(&pl->maps[0], d->Q, 3, dims, str, box);
-  }
-  if (rc == MA_OK) {
-    const uint64_t dims[3] = {128, Hkv, static_cast<uint64_t>(d->max_tot_k)};
-    const uint64_t str[2] = {256, Hkv * 256};
-    const uint32_t box[3] = {64, 1, 128};
-    rc = encode(&pl->maps[1], d->K, 3, dims, str, box);
-    if (rc == MA_OK) rc = encode(&pl->maps[2], d->V, 3, dims, str, box);
-  }
-  if (rc == MA_OK) {
-    const uint64_t dims[2] = {KL, static_cast<uint64_t>(d->max_row_tiles) * 128};
-    const uint64_t str[1] = {KL * 2};
-    const uint32_t box[2] = {64, 128};
-    rc = encode(&pl->maps[3], d->o_scratch, 2, dims, str, box);
-  }
-  if (rc == MA_OK) {
-    const uint64_t dims[2] = {hidden_pad, KL};
-    const uint64_t str[1] = {hidden_pad * 2};
-    const uint32_t box[2] = {64, 64};
-    rc = encode(&pl->maps[4], d->W_o, 2, dims, str, box);
-  }
+  int rc = ma::encode_path_maps(pl->maps, d->Q, d->K, d->V, d->o_scratch, d->W_o, H, Hkv,
+                                static_cast<uint64_t>(d->max_tot_q),
+                                static_cast<uint64_t>(d->max_tot_k),
+                                static_cast<uint64_t>(d->max_row_tiles), hidden_pad);
   if (rc != MA_OK) { delete pl; return rc; }
   *out = pl;
   return MA_OK;

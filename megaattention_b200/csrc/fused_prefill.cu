@@ -32,8 +32,9 @@ namespace {
 constexpr uint32_t kTile = 32768;          // 128 x 128 bf16
 constexpr uint32_t kPanel = 16384;         // 128 rows x 64 bf16 (one 128-byte-swizzle panel)
 constexpr uint32_t kSmQ = 0;               // two Q tiles
-constexpr uint32_t kSmKV = 2 * kTile;      // ring of four K/V tiles
-constexpr uint32_t kOpStage = 16384 + 65536;   // O_proj stage: A 128x64 + W 64x512
+constexpr uint32_t kSmKV = 2 * kTile;      // ring of five K/V tiles
+constexpr int kKvSlots = 5;
+constexpr uint32_t kOpStage = 16384 + 32768;   // O_proj stage: A 128x64 + W 64x256 (4 stages)
 constexpr uint32_t kWPanel = 8192;         // 64 k-rows x 64 n bf16
 constexpr uint32_t kTmemS = 0;             // S0 at 0, S1 at 128 (P aliases the first 64 cols)
 constexpr uint32_t kTmemO = 256;           // O0 at 256, O1 at 384
@@ -42,21 +43,42 @@ constexpr uint32_t kIdescPV = make_idesc_bf16(128, 128, 0, 1);
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
 
 struct Bars {
-  uint64_t q_full[2];
-  uint64_t kv_full[4];
-  uint64_t kv_empty[4];
-  uint64_t s_full[2];
-  uint64_t p_full[2];
-  uint64_t o_done[2];
-  uint64_t op_full[2];
-  uint64_t op_empty[2];
-  uint64_t op_done;
+  uint64_t task_full[2];    // scheduler -> roles: descriptor k is valid        (count 1)
+  uint64_t task_empty[2];   // roles -> scheduler: task in slot k is finished   (count 11)
+  uint64_t loads_done[2];   // producer: every load of the task in slot k is issued (count 1)
+  uint64_t q_full[2];       // TMA: Q tile i landed
+  uint64_t q_empty[2];      // MMA: last Q K^T of the task for tile i completed
+  uint64_t kv_full[kKvSlots];
+  uint64_t kv_empty[kKvSlots];   // both MMA issuers release a slot (count 2)
+  uint64_t s_full[2];       // MMA: S_i ready
+  uint64_t p_full[2];       // softmax threads: P_i written (count 128)
+  uint64_t o_done[2];       // MMA: last P V of the task for tile i completed
+  uint64_t o_free[2];       // epilogue threads: O_i read out (count 128)
+  uint64_t op_full[4];
+  uint64_t op_empty[4];
+  uint64_t acc_full[2];     // MMA: O_proj accumulator half h complete
+  uint64_t acc_free[2];     // epilogue threads: half h read out (count 256)
+  uint64_t dbg;             // trace builds only
 };
 
 struct Env {
   const KParams* p;
   volatile int* abort_flag;
 };
+
+// Optional event trace (compiled in with -DMA_TRACE only): CTA 0 stamps (code, clock) pairs
+// per role into the words that follow the 8 status words.
+#ifdef MA_TRACE
+#define MA_TRACE_DECL(role_id) uint32_t tr_n = 0; const int tr_role = (role_id);
+#define MA_EV(code)                                                                        \
+  if (blockIdx.x == 0 && tr_n < 1000) {                                                    \
+    uint32_t* tb = p.status + 8 + tr_role * 2048 + tr_n * 2;                               \
+    tb[0] = (code); tb[1] = static_cast<uint32_t>(clock64()); ++tr_n;                      \
+  }
+#else
+#define MA_TRACE_DECL(role_id)
+#define MA_EV(code)
+#endif
 
 __device__ __noinline__ void report(const Env& e, uint32_t code, uint32_t site, uint32_t aux) {
   if (atomicCAS(e.p->status, 0u, code) == 0u) {
@@ -71,6 +93,7 @@ __device__ __noinline__ void report(const Env& e, uint32_t code, uint32_t site, 
 // Bounded mbarrier wait.  Returns false once the wait limit passed or the CTA aborted.
 __device__ __forceinline__ bool wait_bar(const Env& e, uint32_t bar, uint32_t parity,
                                          uint32_t site) {
+  if (mbar_try_wait(bar, parity)) return true;
   if (*e.abort_flag) return false;
 #pragma unroll 1
   for (int i = 0; i < 32; ++i)
@@ -267,28 +290,39 @@ __device__ __noinline__ void rank_barrier(const Env& e) {
 }
 
 // ---------------------------------------------------------------- FA: MMA helpers
+constexpr uint64_t kDescK = smem_desc_template(16, 1024);          // K-major, 128-B swizzle
+constexpr uint64_t kDescVmn = smem_desc_template(kPanel, 1024);    // V tile [kv][d], MN-major
+constexpr uint64_t kDescWmn = smem_desc_template(kWPanel, 1024);   // W slab [k][n], MN-major
+
+// S = Q K^T over d = 128: 8 k-steps; both tiles are two 64-wide swizzled panels.
 __device__ __forceinline__ void issue_qk(uint32_t tmem_s, uint32_t sm_q, uint32_t sm_k) {
+  const uint32_t q16 = sm_q >> 4, k16 = sm_k >> 4;
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk) {
-    const uint32_t off = (kk >> 2) * kPanel + (kk & 3) * 32;
-    mma_ss(tmem_s, make_smem_desc(sm_q + off, 16, 1024), make_smem_desc(sm_k + off, 16, 1024),
+    const uint32_t off16 = ((kk >> 2) * kPanel + (kk & 3) * 32) >> 4;
+    mma_ss(tmem_s, smem_desc_at(kDescK, q16 + off16), smem_desc_at(kDescK, k16 + off16),
            kIdescQK, kk > 0);
   }
 }
 // O (+)= P V : P is bf16 in TMEM (8 columns per 16 kv), V tile is [kv][d] in two d panels.
 __device__ __forceinline__ void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t sm_v,
                                          bool acc) {
+  const uint32_t v16 = sm_v >> 4;
 #pragma unroll
-  for (int kk = 0; kk < 8; ++kk) {
-    mma_ts(tmem_o, tmem_p + kk * 8, make_smem_desc(sm_v + kk * 2048, kPanel, 1024), kIdescPV,
+  for (int kk = 0; kk < 8; ++kk)
+    mma_ts(tmem_o, tmem_p + kk * 8, smem_desc_at(kDescVmn, v16 + kk * 128), kIdescPV,
            (acc || kk > 0) ? 1u : 0u);
-  }
 }
 
 }  // namespace
 
-struct TaskFA { int ft, head0, nt, kv_head, q_row0, valid_m, k_start, k_len, offset, nblk, mb; };
-struct TaskOP { int ft, base_out, vnt, valid_m, slot; };
+// Task descriptor words written by the scheduler (shared memory, two slots).
+enum : int { T_MODE = 0, T_FT = 1,
+             TF_HEAD0 = 2, TF_NT = 3, TF_KVH = 4, TF_QROW0 = 5, TF_VALID = 6, TF_KSTART = 7,
+             TF_KLEN = 8, TF_OFFSET = 9, TF_NBLK = 10, TF_MB = 11,
+             TO_BASE = 2, TO_VNT = 3, TO_VALID = 4, TO_SLOT = 5, T_WORDS = 12 };
+
+__device__ __forceinline__ bool is_tile_mode(int m) { return m == MODE_FA || m == MODE_OPROJ; }
 
 __global__ void __launch_bounds__(kThreads, 1)
 fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
@@ -300,8 +334,9 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) Bars bars;
   __shared__ uint32_t s_tmem;
-  __shared__ int s_mode, s_abort;
-  __shared__ int s_task[12];
+  __shared__ int s_abort;
+  __shared__ int s_desc[2][T_WORDS];
+  __shared__ int s_pipe_turn;   // serialises the two issuers' MMA batches (scheduling only)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -311,19 +346,29 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
 
   if (tid == 0) {
     s_abort = 0;
+    s_pipe_turn = 0;
     for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars.task_full[i]), 1);
+      mbar_init(smem_u32(&bars.task_empty[i]), 11);
+      mbar_init(smem_u32(&bars.loads_done[i]), 1);
       mbar_init(smem_u32(&bars.q_full[i]), 1);
+      mbar_init(smem_u32(&bars.q_empty[i]), 1);
       mbar_init(smem_u32(&bars.s_full[i]), 1);
       mbar_init(smem_u32(&bars.p_full[i]), 128);
       mbar_init(smem_u32(&bars.o_done[i]), 1);
+      mbar_init(smem_u32(&bars.o_free[i]), 128);
+      mbar_init(smem_u32(&bars.acc_full[i]), 1);
+      mbar_init(smem_u32(&bars.acc_free[i]), 256);
+    }
+    for (int i = 0; i < kKvSlots; ++i) {
+      mbar_init(smem_u32(&bars.kv_full[i]), 1);
+      mbar_init(smem_u32(&bars.kv_empty[i]), 2);
+    }
+    for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&bars.op_full[i]), 1);
       mbar_init(smem_u32(&bars.op_empty[i]), 1);
     }
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(smem_u32(&bars.kv_full[i]), 1);
-      mbar_init(smem_u32(&bars.kv_empty[i]), 1);
-    }
-    mbar_init(smem_u32(&bars.op_done), 1);
+    mbar_init(smem_u32(&bars.dbg), 1);
     fence_mbar_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -338,142 +383,309 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
   tc_fence_after();
   const uint32_t tmem = s_tmem;
 
-  const int num_fa = p.actv[0];
-  const int total_op = p.actv[1];
-  const int owner_words = p.actv[4];
-  const int local_owned = p.actv[5];
-  int role = 0;
-  {
-    const int wsum = p.w_fa + p.w_oproj + p.w_ar;
-    const int r = static_cast<int>(blockIdx.x) % wsum;
-    role = (r < p.w_fa) ? 0 : (r < p.w_fa + p.w_oproj) ? 1 : 2;
-  }
+  // Every role walks the two descriptor slots in turn.  A role arrives on task_empty[k]
+  // when its part of the task in slot k is finished; the scheduler publishes the task's
+  // completion and refills the slot once all ten arrivals are in, so the scheduler runs
+  // one task ahead of the workers.  Attention tiles and O_proj tiles overlay the same
+  // shared memory and TMEM: a role that goes from one kind to the other first waits for
+  // the previous task to finish completely (same-kind neighbours overlap freely).
+  int slot_k = 0;
+  uint32_t tf_par[2] = {0, 0};
+  uint32_t n_arrived[2] = {0, 0};
+  int prev_mode = MODE_IDLE, prev_k = 0;
 
-  // mbarrier phase bookkeeping; every role advances its own copies in lockstep
-  uint32_t kvc = 0;                 // K/V ring uses (producer and MMA issuer)
-  uint32_t opc = 0;                 // O_proj stage uses (producer and MMA issuer)
-  uint32_t q_par[2] = {0, 0};       // MMA issuer
-  uint32_t p_par[2] = {0, 0};       // MMA issuer
-  uint32_t s_par = 0, o_par = 0;    // compute warpgroup (its own tile)
-  uint32_t d_par = 0;               // compute warpgroups: op_done
+#define MA_NEXT_TASK(desc_ptr, mode_var)                                                   \
+  if (!wait_bar(env, smem_u32(&bars.task_full[slot_k]), tf_par[slot_k], 0x100 + warp)) break; \
+  tf_par[slot_k] ^= 1u;                                                                    \
+  const int* desc_ptr = s_desc[slot_k];                                                    \
+  const int mode_var = desc_ptr[T_MODE];                                                   \
+  if (mode_var == MODE_DONE) break;
+#define MA_DRAIN_IF_SWITCH(mode_var)                                                       \
+  if (is_tile_mode(mode_var) && is_tile_mode(prev_mode) && mode_var != prev_mode)          \
+    wait_bar(env, smem_u32(&bars.task_empty[prev_k]), (n_arrived[prev_k] - 1u) & 1u, 0x110 + warp);
+#define MA_TASK_DONE(mode_var)                                                             \
+  mbar_arrive(smem_u32(&bars.task_empty[slot_k]));                                         \
+  ++n_arrived[slot_k];                                                                     \
+  prev_mode = mode_var; prev_k = slot_k; slot_k ^= 1;
 
-  const int wg = (warp >= 4) ? ((warp - 4) >> 2) : -1;       // compute warpgroup 0 / 1
-  const int row = (warp & 3) * 32 + lane;                    // TMEM lane == tile row
-  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-
-  while (true) {
-    if (tid == 0) {
-      int mode, arg;
-      schedule_pick(env, role, num_fa, total_op, owner_words, local_owned, &mode, &arg);
-      if (mode == MODE_FA) {
-        const int nt = p.pair ? 2 : 1;
-        const int ft = arg / p.H, head0 = arg % p.H;
-        const int b = p.fa_b[ft], mb = p.fa_mb[ft];
-        const int q0 = p.cu_q[b], q_len = p.cu_q[b + 1] - q0;
-        const int k0 = p.cu_k[b], k_len = p.cu_k[b + 1] - k0;
-        const int offset = k_len - q_len;
-        int nblk = (k_len + 127) >> 7;
-        const int nb2 = ((mb + 1) * 128 + offset + 127) >> 7;
-        if (nb2 < nblk) nblk = nb2;
-        s_task[0] = ft; s_task[1] = head0; s_task[2] = nt; s_task[3] = head0 / p.q_per_kv;
-        s_task[4] = q0 + mb * 128;
-        s_task[5] = min(128, q_len - mb * 128);
-        s_task[6] = k0; s_task[7] = k_len; s_task[8] = offset; s_task[9] = nblk; s_task[10] = mb;
-      } else if (mode == MODE_OPROJ || mode == MODE_AR) {
-        const int ft = arg / p.nsg, g = arg % p.nsg;
-        const int base_out = g * p.sg;
-        const int b = p.fa_b[ft], mb = p.fa_mb[ft];
-        const int q_len = p.cu_q[b + 1] - p.cu_q[b];
-        s_task[0] = ft; s_task[1] = base_out; s_task[2] = min(p.sg, p.num_out - base_out);
-        s_task[3] = min(128, q_len - mb * 128); s_task[4] = arg;
-      } else if (mode == MODE_IDLE) {
-        __nanosleep(200);
+  if (warp < 4) {
+    reg_dec<64>();
+    if (warp == 2 && lane == 0) {
+      // ==================================================================== scheduler
+      const int num_fa = p.actv[0];
+      const int total_op = p.actv[1];
+      const int owner_words = p.actv[4];
+      const int local_owned = p.actv[5];
+      int role;
+      {
+        const int wsum = p.w_fa + p.w_oproj + p.w_ar;
+        const int r = static_cast<int>(blockIdx.x) % wsum;
+        role = (r < p.w_fa) ? 0 : (r < p.w_fa + p.w_oproj) ? 1 : 2;
       }
-      s_mode = mode;
-    }
-    __syncthreads();
-    const int mode = s_mode;
-    if (mode == MODE_DONE) break;
-
-    if (mode == MODE_FA) {
-      // ====================================================================== FA
-      const int ft = s_task[0], head0 = s_task[1], nt = s_task[2], kv_head = s_task[3];
-      const int q_row0 = s_task[4], valid_m = s_task[5], k_start = s_task[6];
-      const int k_len = s_task[7], offset = s_task[8], nblk = s_task[9], mb = s_task[10];
-
-      if (warp == 0) {
-        if (lane == 0) {
-          for (int i = 0; i < nt; ++i) {
-            const uint32_t bar = smem_u32(&bars.q_full[i]);
-            const uint32_t dst = smem0 + kSmQ + i * kTile;
-            mbar_expect_tx(bar, kTile);
-            tma_load_3d(dst, &tmQ, bar, 0, head0 + i, q_row0);
-            tma_load_3d(dst + kPanel, &tmQ, bar, 64, head0 + i, q_row0);
+      int k = 0;
+      bool occupied[2] = {false, false};
+      uint32_t te_par[2] = {0, 0}, ld_par[2] = {0, 0};
+      bool ld_pending[2] = {false, false};
+      int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0};
+      auto publish = [&](int kk) {
+        if (s_abort) return;
+        if (occ_mode[kk] == MODE_FA) {
+          fence_acq_rel_gpu();
+          const uint32_t old = atom_add_acqrel_gpu(p.head_ready + occ_a[kk],
+                                                   static_cast<uint32_t>(occ_b[kk]));
+          if (!(p.flags & 1u) && static_cast<int>(old) + occ_b[kk] == p.H)
+            publish_oproj(env, occ_a[kk]);
+          atom_add_release_gpu(p.ctrl + C_FA_DONE, static_cast<uint32_t>(occ_b[kk]));
+        } else if (occ_mode[kk] == MODE_OPROJ) {
+          publish_ar_ready(p, occ_a[kk]);
+        } else if (occ_mode[kk] == MODE_AR) {
+          fence_acq_rel_sys();
+          finish_ar_slot(p, occ_a[kk]);
+        }
+      };
+      while (true) {
+        if (occupied[k]) {
+          wait_bar(env, smem_u32(&bars.task_empty[k]), te_par[k], 0x120 + k);
+          te_par[k] ^= 1u;
+          occupied[k] = false;
+          publish(k);
+        }
+        // A long attention task must not sit claimed behind another one: take the next
+        // task only once the producer has issued the running task's last load (a few
+        // blocks before its end), which keeps the claim order close to greedy.
+        if (ld_pending[k ^ 1]) {
+          wait_bar(env, smem_u32(&bars.loads_done[k ^ 1]), ld_par[k ^ 1], 0x128 + k);
+          ld_par[k ^ 1] ^= 1u;
+          ld_pending[k ^ 1] = false;
+        }
+        int mode, arg;
+        while (true) {
+          schedule_pick(env, role, num_fa, total_op, owner_words, local_owned, &mode, &arg);
+          if (mode != MODE_IDLE) break;
+          const int o = k ^ 1;
+          if (occupied[o] && mbar_try_wait(smem_u32(&bars.task_empty[o]), te_par[o])) {
+            te_par[o] ^= 1u;
+            occupied[o] = false;
+            publish(o);
+          } else {
+            __nanosleep(100);
           }
-          for (int jj = 0; jj < nblk; ++jj) {
-            const int kv_row = k_start + (nblk - 1 - jj) * 128;
+        }
+        int* d = s_desc[k];
+        if (mode == MODE_FA) {
+          const int nt = p.pair ? 2 : 1;
+          const int pos = arg / p.H, head0 = arg % p.H;
+          const int ft = p.fa_order ? p.fa_order[pos] : pos;
+          const int b = p.fa_b[ft], mb = p.fa_mb[ft];
+          const int q0 = p.cu_q[b], q_len = p.cu_q[b + 1] - q0;
+          const int k0 = p.cu_k[b], k_len = p.cu_k[b + 1] - k0;
+          const int offset = k_len - q_len;
+          int nblk = (k_len + 127) >> 7;
+          const int nb2 = ((mb + 1) * 128 + offset + 127) >> 7;
+          if (nb2 < nblk) nblk = nb2;
+          d[T_FT] = ft; d[TF_HEAD0] = head0; d[TF_NT] = nt; d[TF_KVH] = head0 / p.q_per_kv;
+          d[TF_QROW0] = q0 + mb * 128; d[TF_VALID] = min(128, q_len - mb * 128);
+          d[TF_KSTART] = k0; d[TF_KLEN] = k_len; d[TF_OFFSET] = offset; d[TF_NBLK] = nblk;
+          d[TF_MB] = mb;
+          occ_a[k] = ft; occ_b[k] = nt;
+        } else if (mode == MODE_OPROJ || mode == MODE_AR) {
+          const int ft = arg / p.nsg, g = arg % p.nsg;
+          const int base_out = g * p.sg;
+          const int b = p.fa_b[ft], mb = p.fa_mb[ft];
+          const int q_len = p.cu_q[b + 1] - p.cu_q[b];
+          d[T_FT] = ft; d[TO_BASE] = base_out; d[TO_VNT] = min(p.sg, p.num_out - base_out);
+          d[TO_VALID] = min(128, q_len - mb * 128); d[TO_SLOT] = arg;
+          occ_a[k] = arg;
+        }
+        d[T_MODE] = mode;
+        occ_mode[k] = mode;
+        mbar_arrive(smem_u32(&bars.task_full[k]));
+        if (mode == MODE_DONE) break;
+        occupied[k] = true;
+        ld_pending[k] = true;
+        k ^= 1;
+      }
+    } else if (warp == 0 && lane == 0) {
+      // ==================================================================== TMA producer
+      uint32_t kv_slot = 0, kv_ph = 0, opc = 0, q_uses[2] = {0, 0};
+      MA_TRACE_DECL(0)
+      while (true) {
+        MA_NEXT_TASK(d, mode)
+        MA_DRAIN_IF_SWITCH(mode)
+        if (mode == MODE_FA) {
+          const int nt = d[TF_NT], nblk = d[TF_NBLK];
+          for (int i = 0; i < nt; ++i) {
+            wait_bar(env, smem_u32(&bars.q_empty[i]), (q_uses[i] & 1u) ^ 1u, 0x18 + i);
+            ++q_uses[i];
+            const uint32_t bar = smem_u32(&bars.q_full[i]);
+            mbar_expect_tx(bar, kTile);
+            tma_load_4d(smem0 + kSmQ + i * kTile, &tmQ, bar, 0, d[TF_QROW0], 0, d[TF_HEAD0] + i);
+          }
+          const int kvh = d[TF_KVH];
+          int kv_row = d[TF_KSTART] + (nblk - 1) * 128;
+          for (int jj = 0; jj < nblk; ++jj, kv_row -= 128) {
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
-              const uint32_t slot = kvc & 3u;
-              wait_bar(env, smem_u32(&bars.kv_empty[slot]), ((kvc >> 2) & 1u) ^ 1u, 0x10 + slot);
-              const uint32_t bar = smem_u32(&bars.kv_full[slot]);
-              const uint32_t dst = smem0 + kSmKV + slot * kTile;
-              const CUtensorMap* tm = which ? &tmV : &tmK;
+              wait_bar(env, smem_u32(&bars.kv_empty[kv_slot]), kv_ph ^ 1u, 0x10 + kv_slot);
+              MA_EV(60 + which)
+              const uint32_t bar = smem_u32(&bars.kv_full[kv_slot]);
               mbar_expect_tx(bar, kTile);
-              tma_load_3d(dst, tm, bar, 0, kv_head, kv_row);
-              tma_load_3d(dst + kPanel, tm, bar, 64, kv_head, kv_row);
-              ++kvc;
+              tma_load_4d(smem0 + kSmKV + kv_slot * kTile, which ? &tmV : &tmK, bar, 0, kv_row, 0, kvh);
+              if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
+            }
+          }
+        } else if (mode == MODE_OPROJ) {
+          const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT];
+          const int nkc = p.K_local >> 6;
+          fence_proxy_async_global();   // O_scratch was written with ordinary stores
+          for (int h = 0; h * 2 < vnt; ++h) {
+            for (int kc = 0; kc < nkc; ++kc) {
+              const uint32_t st = opc & 3u;
+              wait_bar(env, smem_u32(&bars.op_empty[st]), ((opc >> 2) & 1u) ^ 1u, 0x90 + st);
+              const uint32_t bar = smem_u32(&bars.op_full[st]);
+              const uint32_t a_dst = smem0 + st * kOpStage;
+              // A chunk 128 x 64 and a W slab of 64 k x 256 n (4 panels; panels past the
+              // padded width are filled with zeros)
+              mbar_expect_tx(bar, kPanel + 4u * kWPanel);
+              tma_load_2d(a_dst, &tmO, bar, kc * 64, ft * 128);
+              tma_load_3d(a_dst + kPanel, &tmW, bar, 0, kc * 64, (base_out + 2 * h) * 2);
+              ++opc;
             }
           }
         }
-        __syncwarp();
-      } else if (warp == 1) {
-        if (lane == 0) {
-          for (int i = 0; i < nt; ++i) {
-            wait_bar(env, smem_u32(&bars.q_full[i]), q_par[i], 0x20 + i);
-            q_par[i] ^= 1u;
+        mbar_arrive(smem_u32(&bars.loads_done[slot_k]));
+        MA_TASK_DONE(mode)
+      }
+    } else if ((warp == 1 || warp == 3) && lane == 0) {
+      // ============================================= MMA issuers: warp 1 -> attention tile 0
+      // and every O_proj task, warp 3 -> attention tile 1.  Both follow the K/V ring so a
+      // slot is released only when both tiles are done with it.
+      const int mi = (warp == 1) ? 0 : 1;
+      uint32_t kv_slot = 0, kv_ph = 0, opc = 0;
+      uint32_t q_par = 0, p_par = 0, o_uses = 0, acc_uses[2] = {0, 0};
+      const uint32_t t_s = tmem + kTmemS + mi * 128, t_o = tmem + kTmemO + mi * 128;
+      const uint32_t sm_q = smem0 + kSmQ + mi * kTile;
+      // One tile's batch (P V, then the next Q K^T) is issued as a unit: when both tiles
+      // become ready together the second waits for the first, which staggers the two
+      // softmax warpgroups so that one tile's MMAs run under the other tile's softmax.
+      // The lock only shapes the schedule; giving up on it is harmless.
+      auto pipe_lock = [&]() {
+        for (int it = 0; it < (1 << 16); ++it)
+          if (atomicCAS(&s_pipe_turn, 0, 1) == 0) return;
+      };
+      auto pipe_unlock = [&]() { atomicExch(&s_pipe_turn, 0); };
+      MA_TRACE_DECL(mi == 0 ? 1 : 10)
+      while (true) {
+        MA_NEXT_TASK(d, mode)
+        MA_DRAIN_IF_SWITCH(mode)
+        if (mode == MODE_FA) {
+          const int nblk = d[TF_NBLK];
+          const bool act = mi < d[TF_NT];
+          if (act) {
+            wait_bar(env, smem_u32(&bars.q_full[mi]), q_par, 0x20 + mi);
+            q_par ^= 1u;
           }
-          uint32_t slot_k = kvc & 3u;
-          wait_bar(env, smem_u32(&bars.kv_full[slot_k]), (kvc >> 2) & 1u, 0x30 + slot_k);
-          ++kvc;
-          tc_fence_after();
-          for (int i = 0; i < nt; ++i) {
-            issue_qk(tmem + kTmemS + i * 128, smem0 + kSmQ + i * kTile,
-                     smem0 + kSmKV + slot_k * kTile);
-            tc_commit(smem_u32(&bars.s_full[i]));
+          uint32_t slot_kk = kv_slot;
+          wait_bar(env, smem_u32(&bars.kv_full[slot_kk]), kv_ph, 0x30 + slot_kk);
+          if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
+          if (act) {
+            tc_fence_after();
+            pipe_lock();
+            issue_qk(t_s, sm_q, smem0 + kSmKV + slot_kk * kTile);
+            tc_commit(smem_u32(&bars.s_full[mi]));
+            pipe_unlock();
+            if (nblk == 1) tc_commit(smem_u32(&bars.q_empty[mi]));
           }
-          tc_commit(smem_u32(&bars.kv_empty[slot_k]));
+          tc_commit(smem_u32(&bars.kv_empty[slot_kk]));
           for (int jj = 0; jj < nblk; ++jj) {
-            const uint32_t slot_v = kvc & 3u;
-            wait_bar(env, smem_u32(&bars.kv_full[slot_v]), (kvc >> 2) & 1u, 0x40 + slot_v);
-            ++kvc;
-            const bool has_next = (jj + 1 < nblk);
-            if (has_next) {
-              slot_k = kvc & 3u;
-              wait_bar(env, smem_u32(&bars.kv_full[slot_k]), (kvc >> 2) & 1u, 0x50 + slot_k);
-              ++kvc;
-            }
-            for (int i = 0; i < nt; ++i) {
-              wait_bar(env, smem_u32(&bars.p_full[i]), p_par[i], 0x60 + i);
-              p_par[i] ^= 1u;
-              tc_fence_after();
-              issue_pv(tmem + kTmemO + i * 128, tmem + kTmemS + i * 128,
-                       smem0 + kSmKV + slot_v * kTile, jj > 0);
-              if (!has_next) {
-                tc_commit(smem_u32(&bars.o_done[i]));
-              } else {
-                issue_qk(tmem + kTmemS + i * 128, smem0 + kSmQ + i * kTile,
-                         smem0 + kSmKV + slot_k * kTile);
-                tc_commit(smem_u32(&bars.s_full[i]));
+            const uint32_t slot_v = kv_slot;
+            wait_bar(env, smem_u32(&bars.kv_full[slot_v]), kv_ph, 0x40 + slot_v);
+            if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
+            MA_EV(12)
+            if (act) {
+              if (jj == 0) {   // the previous task's epilogue must have read O out
+                wait_bar(env, smem_u32(&bars.o_free[mi]), (o_uses & 1u) ^ 1u, 0x68 + mi);
+                ++o_uses;
               }
+              wait_bar(env, smem_u32(&bars.p_full[mi]), p_par, 0x60 + mi);
+              p_par ^= 1u;
+              MA_EV(10)
+              tc_fence_after();
             }
-            tc_commit(smem_u32(&bars.kv_empty[slot_v]));
-            if (has_next) tc_commit(smem_u32(&bars.kv_empty[slot_k]));
+            const bool has_next = (jj + 1 < nblk);
+            if (has_next) {          // K of the next block: prefetched long ago
+              slot_kk = kv_slot;
+              wait_bar(env, smem_u32(&bars.kv_full[slot_kk]), kv_ph, 0x50 + slot_kk);
+              if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
+            }
+            MA_EV(13)
+            if (act) {
+              pipe_lock();
+              MA_EV(14)
+              issue_pv(t_o, t_s, smem0 + kSmKV + slot_v * kTile, jj > 0);
+              tc_commit(smem_u32(&bars.kv_empty[slot_v]));
+              if (has_next) {
+                issue_qk(t_s, sm_q, smem0 + kSmKV + slot_kk * kTile);
+                tc_commit(smem_u32(&bars.s_full[mi]));
+                pipe_unlock();
+                MA_EV(20)
+                tc_commit(smem_u32(&bars.kv_empty[slot_kk]));
+                if (jj + 2 == nblk) tc_commit(smem_u32(&bars.q_empty[mi]));
+              } else {
+                tc_commit(smem_u32(&bars.o_done[mi]));
+                pipe_unlock();
+              }
+            } else {
+              tc_commit(smem_u32(&bars.kv_empty[slot_v]));
+              if (has_next) tc_commit(smem_u32(&bars.kv_empty[slot_kk]));
+            }
+          }
+        } else if (mode == MODE_OPROJ && mi == 0) {
+          const int vnt = d[TO_VNT];
+          const int nkc = p.K_local >> 6;
+          for (int h = 0; h * 2 < vnt; ++h) {
+            const int ncols = min(2, vnt - 2 * h) * 128;
+            const uint32_t idesc = make_idesc_bf16(128, ncols, 0, 1);
+            wait_bar(env, smem_u32(&bars.acc_free[h]), (acc_uses[h] & 1u) ^ 1u, 0xA8 + h);
+            ++acc_uses[h];
+            for (int kc = 0; kc < nkc; ++kc) {
+              const uint32_t st = opc & 3u;
+              wait_bar(env, smem_u32(&bars.op_full[st]), (opc >> 2) & 1u, 0xA0 + st);
+              ++opc;
+              MA_EV(40)
+              tc_fence_after();
+              const uint32_t a16 = (smem0 + st * kOpStage) >> 4;
+              const uint32_t w16 = a16 + (kPanel >> 4);
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                mma_ss(tmem + h * 256, smem_desc_at(kDescK, a16 + kk * 2),
+                       smem_desc_at(kDescWmn, w16 + kk * 128), idesc,
+                       (kc > 0 || kk > 0) ? 1u : 0u);
+              tc_commit(smem_u32(&bars.op_empty[st]));
+            }
+            tc_commit(smem_u32(&bars.acc_full[h]));
+            MA_EV(41)
           }
         }
-        __syncwarp();
-      } else if (wg >= 0 && wg < nt) {
-        // ------------------------------------------------ softmax + epilogue of tile `wg`
+        MA_TASK_DONE(mode)
+      }
+    }
+    __syncwarp();
+  } else {
+    // ====================================================================== compute warps
+    reg_inc<216>();
+    const int wg = (warp - 4) >> 2;                            // compute warpgroup 0 / 1
+    const int row = (warp & 3) * 32 + lane;                    // TMEM lane == tile row
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint32_t s_par = 0, o_par = 0, acc_par[2] = {0, 0};
+    MA_TRACE_DECL(2 + (warp - 4))
+    while (true) {
+      MA_NEXT_TASK(d, mode)
+      if (lane == 0) { MA_EV(1000 + mode) }
+      if (mode == MODE_FA && wg < d[TF_NT]) {
+        // -------------------------------------------- softmax + epilogue of tile `wg`
+        const int ft = d[T_FT], head = d[TF_HEAD0] + wg, valid_m = d[TF_VALID];
+        const int k_len = d[TF_KLEN], offset = d[TF_OFFSET], nblk = d[TF_NBLK], mb = d[TF_MB];
         const uint32_t t_s = tmem + kTmemS + wg * 128 + lane_base;
         const uint32_t t_o = tmem + kTmemO + wg * 128 + lane_base;
         const uint32_t bar_s = smem_u32(&bars.s_full[wg]);
@@ -487,30 +699,28 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           const int j = nblk - 1 - jj;
           wait_bar(env, bar_s, s_par, 0x70 + wg);
           s_par ^= 1u;
+          if (lane == 0) { MA_EV(30) }
           tc_fence_after();
           uint32_t s[4][32];
 #pragma unroll
           for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
           tc_wait_ld();
+          if (lane == 0) { MA_EV(31) }
           const bool need_mask = ((j + 1) * 128 - 1 > mb * 128 + offset) || ((j + 1) * 128 > k_len);
-          float m_blk = -INFINITY;
           if (need_mask) {
             const int lim = lim_abs - j * 128;    // columns > lim are masked
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
-              for (int k = 0; k < 32; ++k) {
-                float v = __uint_as_float(s[c][k]);
-                v = (c * 32 + k <= lim) ? v : -INFINITY;
-                s[c][k] = __float_as_uint(v);
-                m_blk = fmaxf(m_blk, v);
-              }
-          } else {
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-              for (int k = 0; k < 32; ++k) m_blk = fmaxf(m_blk, __uint_as_float(s[c][k]));
+              for (int kx = 0; kx < 32; ++kx)
+                if (c * 32 + kx > lim) s[c][kx] = 0xff800000u;   // -inf
           }
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int kx = 0; kx < 32; ++kx)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) mx[c] = fmaxf(mx[c], __uint_as_float(s[c][kx]));
+          const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
           // lazy rescale: move the reference max only when it would grow by > 2^8
           const bool grow = (m_blk > -INFINITY) &&
                             ((m_ref == -INFINITY) || ((m_blk - m_ref) * sl2 > kRescaleThreshold));
@@ -521,7 +731,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             l_run *= o_scale;
           }
           if (jj > 0 && __any_sync(0xffffffffu, grow)) {
-            // the PV MMA of the previous block completed before this block's S was
+            // the P V MMA of the previous block completed before this block's S was
             // committed (in-order tensor pipe), so O is quiescent here
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
@@ -529,193 +739,164 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
               tmem_ld32(t_o + c * 32, o);
               tc_wait_ld();
 #pragma unroll
-              for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * o_scale);
+              for (int kx = 0; kx < 32; ++kx)
+                o[kx] = __float_as_uint(__uint_as_float(o[kx]) * o_scale);
               tmem_st32(t_o + c * 32, o);
             }
           }
+          if (lane == 0) { MA_EV(32) }
           const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * sl2;
-          float sum0 = 0.f, sum1 = 0.f;
+          float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t pk[16];
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const float e0 = ex2(fmaf(__uint_as_float(s[c][2 * k]), sl2, neg_m));
-              const float e1 = ex2(fmaf(__uint_as_float(s[c][2 * k + 1]), sl2, neg_m));
-              sum0 += e0; sum1 += e1;
-              pk[k] = pack_bf16x2(e0, e1);
+            for (int kx = 0; kx < 16; ++kx) {
+              const float e0 = ex2(fmaf(__uint_as_float(s[c][2 * kx]), sl2, neg_m));
+              const float e1 = ex2(fmaf(__uint_as_float(s[c][2 * kx + 1]), sl2, neg_m));
+              sum[(kx & 1) * 2] += e0; sum[(kx & 1) * 2 + 1] += e1;
+              pk[kx] = pack_bf16x2(e0, e1);
             }
-            // 16 packed columns per 32 scores; reuse the 32-wide store as two halves
+            // 16 packed columns per 32 scores: two chunks fill one 32-column store
             if ((c & 1) == 0) {
 #pragma unroll
-              for (int k = 0; k < 16; ++k) s[c][k] = pk[k];
+              for (int kx = 0; kx < 16; ++kx) s[c][kx] = pk[kx];
             } else {
 #pragma unroll
-              for (int k = 0; k < 16; ++k) s[c - 1][16 + k] = pk[k];
+              for (int kx = 0; kx < 16; ++kx) s[c - 1][16 + kx] = pk[kx];
+              tmem_st32(t_s + (c >> 1) * 32, s[c - 1]);
             }
           }
-          l_run += sum0 + sum1;
-          tmem_st32(t_s, s[0]);
-          tmem_st32(t_s + 32, s[2]);
+          l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+          if (lane == 0) { MA_EV(33) }
           tc_wait_st();
           tc_fence_before();
           mbar_arrive(bar_p);
+          if (lane == 0) { MA_EV(34) }
         }
         // epilogue: O / l -> bf16 -> O_scratch[ft, row, head, :]; tail rows are zeros
         wait_bar(env, smem_u32(&bars.o_done[wg]), o_par, 0x80 + wg);
         o_par ^= 1u;
+        if (lane == 0) { MA_EV(35) }
         tc_fence_after();
         const float inv = (row < valid_m && l_run > 0.f) ? (1.f / l_run) : 0.f;
-        uint16_t* dst = p.o_scratch +
-            (static_cast<size_t>(ft * 128 + row) * p.H + (head0 + wg)) * 128;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          tmem_ld32(t_o + c * 32, o);
-          tc_wait_ld();
-          uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+        uint16_t* dst = p.o_scratch + (static_cast<size_t>(ft * 128 + row) * p.H + head) * 128;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
-            v.y = pack_bf16x2(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
-            v.z = pack_bf16x2(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
-            v.w = pack_bf16x2(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
-            d4[q] = v;
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t o[2][32];
+          tmem_ld32(t_o + hh * 64, o[0]);
+          tmem_ld32(t_o + hh * 64 + 32, o[1]);
+          tc_wait_ld();
+          if (hh == 1) {            // all of O_i is in registers: the next task may overwrite it
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bars.o_free[wg]));
+          }
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst + hh * 64 + c * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(o[c][8 * q + 0]) * inv, __uint_as_float(o[c][8 * q + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(o[c][8 * q + 2]) * inv, __uint_as_float(o[c][8 * q + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(o[c][8 * q + 4]) * inv, __uint_as_float(o[c][8 * q + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(o[c][8 * q + 6]) * inv, __uint_as_float(o[c][8 * q + 7]) * inv);
+              d4[q] = v;
+            }
           }
         }
-        tc_fence_before();
         __threadfence();
         fence_proxy_async_global();   // O_scratch is read back by TMA (async proxy)
-      }
-      __syncthreads();
-      if (tid == 0 && !s_abort) {
-        fence_acq_rel_gpu();
-        const uint32_t old = atom_add_acqrel_gpu(p.head_ready + ft, static_cast<uint32_t>(nt));
-        if (!(p.flags & 1u) && static_cast<int>(old) + nt == p.H) publish_oproj(env, ft);
-        atom_add_release_gpu(p.ctrl + C_FA_DONE, static_cast<uint32_t>(nt));
-      }
-    } else if (mode == MODE_OPROJ) {
-      // ====================================================================== O_proj
-      const int ft = s_task[0], base_out = s_task[1], vnt = s_task[2], valid_m = s_task[3];
-      const int slot = s_task[4];
-      const int nkc = p.K_local >> 6;
-      if (warp == 0) {
-        if (lane == 0) {
-          fence_proxy_async_global();
-          for (int kc = 0; kc < nkc; ++kc) {
-            const uint32_t st = opc & 1u;
-            wait_bar(env, smem_u32(&bars.op_empty[st]), ((opc >> 1) & 1u) ^ 1u, 0x90 + st);
-            const uint32_t bar = smem_u32(&bars.op_full[st]);
-            const uint32_t a_dst = smem0 + st * kOpStage;
-            mbar_expect_tx(bar, kPanel + static_cast<uint32_t>(vnt) * 2u * kWPanel);
-            tma_load_2d(a_dst, &tmO, bar, kc * 64, ft * 128);
-            for (int pn = 0; pn < vnt * 2; ++pn)
-              tma_load_2d(a_dst + kPanel + pn * kWPanel, &tmW, bar, base_out * 128 + pn * 64,
-                          kc * 64);
-            ++opc;
-          }
-        }
-        __syncwarp();
-      } else if (warp == 1) {
-        if (lane == 0) {
-          for (int kc = 0; kc < nkc; ++kc) {
-            const uint32_t st = opc & 1u;
-            wait_bar(env, smem_u32(&bars.op_full[st]), (opc >> 1) & 1u, 0xA0 + st);
-            ++opc;
-            tc_fence_after();
-            const uint32_t a_sm = smem0 + st * kOpStage;
-            const uint32_t w_sm = a_sm + kPanel;
+        if (lane == 0) { MA_EV(36) }
+      } else if (mode == MODE_OPROJ) {
+        const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT], valid_m = d[TO_VALID];
+        for (int h = 0; h * 2 < vnt; ++h) {
+          wait_bar(env, smem_u32(&bars.acc_full[h]), acc_par[h], 0xB0 + h);
+          acc_par[h] ^= 1u;
+          if (lane == 0) { MA_EV(50 + h) }
+          tc_fence_after();
+          const int o_t = 2 * h + wg;                   // column tile inside the super-group
+          if (o_t < vnt) {
+            const int out_n = base_out + o_t;
+            uint16_t* dst = p.csym + ((static_cast<size_t>(ft * 128 + row) * p.num_out + out_n) * 128);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint64_t adesc = make_smem_desc(a_sm + kk * 32, 16, 1024);
-              for (int ng = 0; ng * 2 < vnt; ++ng) {
-                const int ncols = min(256, vnt * 128 - ng * 256);
-                const uint64_t bdesc =
-                    make_smem_desc(w_sm + ng * 4 * kWPanel + kk * 2048, kWPanel, 1024);
-                mma_ss(tmem + ng * 256, adesc, bdesc, make_idesc_bf16(128, ncols, 0, 1),
-                       (kc > 0 || kk > 0) ? 1u : 0u);
+            for (int hh = 0; hh < 2; ++hh) {
+              uint32_t r[2][32];
+              tmem_ld32(tmem + lane_base + h * 256 + wg * 128 + hh * 64, r[0]);
+              tmem_ld32(tmem + lane_base + h * 256 + wg * 128 + hh * 64 + 32, r[1]);
+              tc_wait_ld();
+              if (hh == 1) {
+                tc_fence_before();
+                mbar_arrive(smem_u32(&bars.acc_free[h]));
               }
-            }
-            tc_commit(smem_u32(&bars.op_empty[st]));
-          }
-          tc_commit(smem_u32(&bars.op_done));
-        }
-        __syncwarp();
-      } else if (wg >= 0) {
-        wait_bar(env, smem_u32(&bars.op_done), d_par, 0xB0);
-        d_par ^= 1u;
-        tc_fence_after();
-        for (int oo = 0; oo < 2; ++oo) {
-          const int o_t = wg * 2 + oo;                  // column tile inside the super-group
-          if (o_t >= vnt) break;
-          const int out_n = base_out + o_t;
-          uint16_t* dst = p.csym +
-              ((static_cast<size_t>(ft * 128 + row) * p.num_out + out_n) * 128);
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tmem + lane_base + o_t * 128 + c * 32, r);
-            tc_wait_ld();
-            const int col0 = out_n * 128 + c * 32;
-            if (row < valid_m) {
-              if (col0 + 32 <= p.hidden) {
-                uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  uint4 v;
-                  v.x = pack_bf16x2(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
-                  v.y = pack_bf16x2(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
-                  v.z = pack_bf16x2(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
-                  v.w = pack_bf16x2(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
-                  d4[q] = v;
+              for (int c = 0; c < 2; ++c) {
+                const int col0 = out_n * 128 + hh * 64 + c * 32;
+                if (row < valid_m) {
+                  if (col0 + 32 <= p.hidden) {
+                    uint4* d4 = reinterpret_cast<uint4*>(dst + hh * 64 + c * 32);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                      uint4 v;
+                      v.x = pack_bf16x2(__uint_as_float(r[c][8 * q + 0]), __uint_as_float(r[c][8 * q + 1]));
+                      v.y = pack_bf16x2(__uint_as_float(r[c][8 * q + 2]), __uint_as_float(r[c][8 * q + 3]));
+                      v.z = pack_bf16x2(__uint_as_float(r[c][8 * q + 4]), __uint_as_float(r[c][8 * q + 5]));
+                      v.w = pack_bf16x2(__uint_as_float(r[c][8 * q + 6]), __uint_as_float(r[c][8 * q + 7]));
+                      d4[q] = v;
+                    }
+                  } else {
+#pragma unroll
+                    for (int kx = 0; kx < 32; ++kx)
+                      if (col0 + kx < p.hidden)
+                        dst[hh * 64 + c * 32 + kx] = static_cast<uint16_t>(
+                            pack_bf16x2(__uint_as_float(r[c][kx]), 0.f) & 0xFFFFu);
+                  }
                 }
-              } else {
-#pragma unroll
-                for (int k = 0; k < 32; ++k)
-                  if (col0 + k < p.hidden)
-                    dst[c * 32 + k] =
-                        static_cast<uint16_t>(pack_bf16x2(__uint_as_float(r[k]), 0.f) & 0xFFFFu);
               }
             }
+          } else {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bars.acc_free[h]));
           }
         }
-        tc_fence_before();
         if (p.tp > 1) __threadfence_system(); else __threadfence();
-      }
-      __syncthreads();
-      if (tid == 0 && !s_abort) publish_ar_ready(p, slot);
-    } else if (mode == MODE_AR) {
-      // ====================================================================== AllReduce
-      const int ft = s_task[0], base_out = s_task[1], vnt = s_task[2], slot = s_task[4];
-      const int total = vnt * 2048;                    // 16-byte chunks in the slot
-      for (int c0 = tid; c0 < total; c0 += kThreads * 4) {
-        uint4 v[4];
-        unsigned long long a[4];
+        if (lane == 0) { MA_EV(52) }
+      } else if (mode == MODE_AR) {
+        const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT];
+        const int total = vnt * 2048;                    // 16-byte chunks in the slot
+        const int ctid = tid - 128;
+        for (int c0 = ctid; c0 < total; c0 += 256 * 4) {
+          uint4 v[4];
+          unsigned long long a[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int c = c0 + u * kThreads;
-          const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
-          const size_t elem =
-              ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
-          a[u] = p.csym_mc + elem * 2;
-          if (c < total) v[u] = multimem_ld_reduce_bf16x8(a[u]);
+          for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u * 256;
+            const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
+            const size_t elem =
+                ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
+            a[u] = p.csym_mc + elem * 2;
+            if (c < total) v[u] = multimem_ld_reduce_bf16x8(a[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (c0 + u * 256 < total) multimem_st_b128(a[u], v[u]);
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (c0 + u * kThreads < total) multimem_st_b128(a[u], v[u]);
+        __threadfence_system();
       }
-      __threadfence_system();
-      __syncthreads();
-      if (tid == 0) finish_ar_slot(p, slot);
-    } else {
-      __syncthreads();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars.task_empty[slot_k]));
+      ++n_arrived[slot_k];
+      prev_mode = mode; prev_k = slot_k; slot_k ^= 1;
     }
   }
+#undef MA_NEXT_TASK
+#undef MA_DRAIN_IF_SWITCH
+#undef MA_TASK_DONE
 
   // ------------------------------------------------------------------ exit protocol
   // quiesce -> every CTA clears the per-launch control state at full capacity -> all
   // cleared -> (tp > 1) one cross-rank barrier, which also opens the next launch
+  __syncthreads();
   if (!s_abort) {
     grid_sync(env, S_GS_QUIESCE);
     if (!s_abort) {

@@ -46,6 +46,7 @@ struct KParams {
   const int* cu_k;
   const int* fa_b;
   const int* fa_mb;
+  const int* fa_order;            // row tiles in claim order (longest first), or null
   uint32_t* status;
 
   unsigned long long csym_mc;
@@ -55,6 +56,6 @@ struct KParams {
 };
 
 constexpr int kThreads = 384;
-constexpr int kSmemDynamic = 65536 + 4 * 32768 + 1024;   // Q x2, K/V ring x4, align slack
+constexpr int kSmemDynamic = 65536 + 5 * 32768 + 1024;   // Q x2, K/V ring x5, align slack
 
 }  // namespace ma

@@ -13,8 +13,9 @@
 namespace ma {
 cudaError_t launch_fused_prefill(const CUtensorMap* maps, const KParams& kp, int num_ctas,
                                  cudaStream_t stream);
-int encode_bf16_map(CUtensorMap* out, uint64_t base, int rank, const uint64_t* dims,
-                    const uint64_t* strides_bytes, const uint32_t* box);
+int encode_path_maps(CUtensorMap* maps, uint64_t Q, uint64_t K, uint64_t V, uint64_t oscr,
+                     uint64_t W, uint64_t H, uint64_t Hkv, uint64_t tot_q, uint64_t tot_k,
+                     uint64_t row_tiles, uint64_t w_width);
 }  // namespace ma
 
 namespace {
@@ -62,7 +63,7 @@ int scratch_for_current_device(unsigned char** out) {
 extern "C" int ma_fused_prefill_noalloc(const ma_noalloc_args* a, void* stream_) {
   if (!a || !a->seqlens_q || !a->Q || !a->K || !a->V || !a->W_o || !a->out) return MA_ERR_INVALID;
   if (a->H_local < 1 || a->H_kv < 1 || a->H_local % a->H_kv) return MA_ERR_INVALID;
-  if (a->hidden < 8 || a->hidden % 8) return MA_ERR_INVALID;
+  if (a->hidden < 64 || a->hidden % 64) return MA_ERR_INVALID;
   if (a->super_group_n_tiles < 1 || a->super_group_n_tiles > 4) return MA_ERR_INVALID;
   if (a->num_batch < 1) return MA_ERR_INVALID;
   if (a->num_batch > MA_NOALLOC_MAX_BATCH) return MA_ERR_CAPACITY;
@@ -155,33 +156,11 @@ extern "C" int ma_fused_prefill_noalloc(const ma_noalloc_args* a, void* stream_)
 
   // ---- TMA descriptors over the caller's tensors and the scratch (host-side encoding)
   CUtensorMap maps[5];
-  const uint64_t H = a->H_local, Hkv = a->H_kv, KL = K_local;
-  {
-    const uint64_t dims[3] = {128, H, static_cast<uint64_t>(tq)};
-    const uint64_t str[2] = {256, H * 256};
-    const uint32_t box[3] = {64, 1, 128};
-    rc = ma::encode_bf16_map(&maps[0], a->Q, 3, dims, str, box);
-  }
-  if (rc == MA_OK) {
-    const uint64_t dims[3] = {128, Hkv, static_cast<uint64_t>(tk)};
-    const uint64_t str[2] = {256, Hkv * 256};
-    const uint32_t box[3] = {64, 1, 128};
-    rc = ma::encode_bf16_map(&maps[1], a->K, 3, dims, str, box);
-    if (rc == MA_OK) rc = ma::encode_bf16_map(&maps[2], a->V, 3, dims, str, box);
-  }
-  if (rc == MA_OK) {
-    const uint64_t dims[2] = {KL, static_cast<uint64_t>(R) * 128};
-    const uint64_t str[1] = {KL * 2};
-    const uint32_t box[2] = {64, 128};
-    rc = ma::encode_bf16_map(&maps[3], reinterpret_cast<uint64_t>(k.o_scratch), 2, dims, str, box);
-  }
-  if (rc == MA_OK) {
-    // columns past `hidden` are filled with zeros by the TMA unit: no padded copy of W_o
-    const uint64_t dims[2] = {static_cast<uint64_t>(a->hidden), KL};
-    const uint64_t str[1] = {static_cast<uint64_t>(a->hidden) * 2};
-    const uint32_t box[2] = {64, 64};
-    rc = ma::encode_bf16_map(&maps[4], a->W_o, 2, dims, str, box);
-  }
+  // W_o is read in 64-column panels straight from the caller's tensor: hidden % 64 == 0
+  rc = ma::encode_path_maps(maps, a->Q, a->K, a->V, reinterpret_cast<uint64_t>(k.o_scratch), a->W_o,
+                            static_cast<uint64_t>(a->H_local), static_cast<uint64_t>(a->H_kv),
+                            static_cast<uint64_t>(tq), static_cast<uint64_t>(tk),
+                            static_cast<uint64_t>(R), static_cast<uint64_t>(a->hidden));
   if (rc != MA_OK) return rc;
 
   int n = a->num_ctas > 0 ? a->num_ctas : sms;

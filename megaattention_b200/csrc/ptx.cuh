@@ -75,6 +75,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -141,6 +149,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   d |= static_cast<uint64_t>(1) << 46;   // descriptor version (Blackwell)
   d |= static_cast<uint64_t>(2) << 61;   // SWIZZLE_128B
   return d;
+}
+
+// Same descriptor from parts: `tmpl` holds everything but the start address (see
+// smem_desc_template), `addr16` is the shared address >> 4.  Cheap enough to rebuild per MMA.
+__host__ __device__ constexpr uint64_t smem_desc_template(uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) |
+         (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+}
+__device__ __forceinline__ uint64_t smem_desc_at(uint64_t tmpl, uint32_t addr16) {
+  return tmpl | static_cast<uint64_t>(addr16 & 0x3FFFu);
 }
 
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.

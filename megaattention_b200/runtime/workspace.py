@@ -29,7 +29,20 @@ from ..metadata.row_desc import active_counts, oproj_task_counts
 
 NUM_CTRL = 8
 NUM_SYNC = 3
-NUM_STATUS = 8
+NUM_STATUS = 8 + 11 * 2048     # 8 status words + room for the optional event trace
+
+
+def claim_order(meta) -> np.ndarray:
+    """Row tiles sorted by the number of 128-key blocks their attention task visits,
+    longest first (stable), so the biggest tasks are claimed first and the tail of the
+    launch is filled with small ones.  Same on every rank."""
+    M = meta.M_TILE
+    b = meta.batch_idx.astype(np.int64)
+    lq = np.diff(meta.cu_seqlens_q.astype(np.int64))[b]
+    lk = np.diff(meta.cu_seqlens_k.astype(np.int64))[b]
+    last_row = (meta.m_block.astype(np.int64) + 1) * M + (lk - lq)
+    nblk = np.minimum(-(-lk // M), -(-last_row // M))
+    return np.argsort(-nblk, kind="stable").astype(np.int32)
 
 
 class FusedFaOprojArWorkspace:
@@ -113,6 +126,7 @@ class FusedFaOprojArWorkspace:
             cu_k=zeros(max_num_batch + 1, torch.int32),
             fa_b=zeros(max_num_row_tiles, torch.int32),
             fa_mb=zeros(max_num_row_tiles, torch.int32),
+            fa_order=zeros(max_num_row_tiles, torch.int32),
             Q=zeros((tot_cap, H_local, D), dtype),
             K=zeros((max_tot_k, H_kv, D), dtype),
             V=zeros((max_tot_k, H_kv, D), dtype),
@@ -159,7 +173,8 @@ class FusedFaOprojArWorkspace:
                         ("ready_count", self.rco), ("ready_bits", self.rbits),
                         ("ar_done_bits", self.ar_done_bits), ("nvl_signal", self.nvl),
                         ("cu_q", self.cu_q), ("cu_k", self.cu_k), ("fa_b", self.fa_b),
-                        ("fa_mb", self.fa_mb), ("status", self.status)):
+                        ("fa_mb", self.fa_mb), ("status", self.status),
+                        ("fa_order", self.fa_order)):
             setattr(d, name, t.data_ptr())
         d.csym_multicast = self.csym_mc_ptr
         for r in range(self.tp_size if self.tp_size > 1 else 0):
@@ -210,18 +225,19 @@ class FusedFaOprojArWorkspace:
 
     def _set_meta(self, meta):
         R, nb = meta.num_row_tiles, meta.num_batch
-        # one small H2D copy: cu_q | cu_k | fa_b | fa_mb | actv packed on the host
+        # one small H2D copy: cu_q | cu_k | fa_b | fa_mb | fa_order | actv packed on the host
         host = np.concatenate([
             np.asarray(meta.cu_seqlens_q, dtype=np.int32),
             np.asarray(meta.cu_seqlens_k, dtype=np.int32),
             np.asarray(meta.batch_idx, dtype=np.int32),
             np.asarray(meta.m_block, dtype=np.int32),
+            claim_order(meta),
             active_counts(R, self.H_local, self.num_super_groups, self.tp_size, self.rank),
         ])
         stage = torch.from_numpy(host).to(self.dev, non_blocking=False)
         o = 0
         for dst, n in ((self.cu_q, nb + 1), (self.cu_k, nb + 1), (self.fa_b, R),
-                       (self.fa_mb, R), (self.actv, 6)):
+                       (self.fa_mb, R), (self.fa_order, R), (self.actv, 6)):
             dst[:n].copy_(stage[o:o + n])
             o += n
         self._meta = meta
@@ -266,7 +282,7 @@ class FusedFaOprojArWorkspace:
         """Fault localisation only; never on the production / bench / test default path.
         With tp > 1 every rank must call it, followed by a host barrier."""
         for t in (self.ctrl, self.sync_ctrl, self.actv, self.head_ready, self.oproj_queue,
-                  self.rco, self.rbits, self.ar_done_bits, self.nvl, self.csym, self.Oscr,
+                  self.fa_order, self.rco, self.rbits, self.ar_done_bits, self.nvl, self.csym, self.Oscr,
                   self.status):
             t.zero_()
 

@@ -100,5 +100,5 @@ def test_noalloc_refuses_sizes_beyond_its_scratch():
     # more row tiles than the descriptor table holds
     rc, _ = _call([128] * 513, None, 1, 1, 128, dummy, dummy, dummy, dummy, dummy)
     assert rc == _cabi.MA_ERR_CAPACITY
-    rc, _ = _call([128], None, 2, 1, 100, dummy, dummy, dummy, dummy, dummy)   # hidden % 8
+    rc, _ = _call([128], None, 2, 1, 100, dummy, dummy, dummy, dummy, dummy)   # hidden % 64
     assert rc == _cabi.MA_ERR_INVALID
