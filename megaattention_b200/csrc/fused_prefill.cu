@@ -122,14 +122,29 @@ __device__ __forceinline__ bool try_fa(const KParams& p, int num_fa, int* arg) {
   return false;
 }
 
-__device__ __forceinline__ bool try_pop_oproj(const KParams& p, int* arg) {
-  const uint32_t head = ld_relaxed_gpu(p.ctrl + C_OP_CONSUME);
-  const uint32_t tail = ld_acquire_gpu(p.ctrl + C_OP_PUBLISH);
-  if (head < tail && atom_cas_relaxed_gpu(p.ctrl + C_OP_CONSUME, head, head + 1) == head) {
-    *arg = static_cast<int>(ld_relaxed_gpu(p.oproj_queue + head));
-    return true;
+// Pop from the published O_proj ready queue.  The reference pops with a CAS on the consume
+// index (fused_fa_oproj_ar.py:168-189); with one CTA per SM all polling, a CAS admits one
+// winner per L2 round trip and the queue drains at ~2 tasks/us.  Here a CTA takes a ticket
+// with one atomicAdd (every attempt succeeds) after seeing head < tail.  A ticket that lost
+// the race to a not-yet-published entry stays pending in this CTA (at most one) and is
+// served as soon as the publish index passes it; meanwhile the CTA keeps taking other work.
+__device__ __forceinline__ bool try_pop_oproj(const KParams& p, int total_op, int* pending,
+                                              int* arg) {
+  if (*pending < 0) {
+    const uint32_t head = ld_relaxed_gpu(p.ctrl + C_OP_CONSUME);
+    const uint32_t tail = ld_acquire_gpu(p.ctrl + C_OP_PUBLISH);
+    if (head >= tail) return false;
+    const uint32_t t = atom_add_relaxed_gpu(p.ctrl + C_OP_CONSUME, 1u);
+    if (static_cast<int>(t) >= total_op) return false;    // past the end: nothing there
+    *pending = static_cast<int>(t);
+    if (t >= tail && static_cast<uint32_t>(*pending) >= ld_acquire_gpu(p.ctrl + C_OP_PUBLISH))
+      return false;
+  } else if (static_cast<uint32_t>(*pending) >= ld_acquire_gpu(p.ctrl + C_OP_PUBLISH)) {
+    return false;
   }
-  return false;
+  *arg = static_cast<int>(ld_relaxed_gpu(p.oproj_queue + *pending));
+  *pending = -1;
+  return true;
 }
 
 __device__ __forceinline__ bool try_claim_ar(const KParams& p, int owner_words, int local_owned,
@@ -155,8 +170,8 @@ __device__ __forceinline__ bool try_claim_ar(const KParams& p, int owner_words, 
 }
 
 __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, int total_op,
-                                           int owner_words, int local_owned, int* mode,
-                                           int* arg) {
+                                           int owner_words, int local_owned, int* pending,
+                                           int* mode, int* arg) {
   const KParams& p = *e.p;
   *mode = MODE_IDLE;
   *arg = -1;
@@ -181,7 +196,7 @@ __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, i
     bool ok = false;
     if (m == MODE_FA) ok = try_fa(p, num_fa, arg);
     else if (fa_only) ok = false;
-    else if (m == MODE_OPROJ) ok = try_pop_oproj(p, arg);
+    else if (m == MODE_OPROJ) ok = try_pop_oproj(p, total_op, pending, arg);
     else if (p.tp > 1) ok = try_claim_ar(p, owner_words, local_owned, arg);
     if (ok) { *mode = m; return; }
   }
@@ -426,6 +441,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       bool occupied[2] = {false, false};
       uint32_t te_par[2] = {0, 0}, ld_par[2] = {0, 0};
       bool ld_pending[2] = {false, false};
+      int pending_ticket = -1;
       int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0};
       auto publish = [&](int kk) {
         if (s_abort) return;
@@ -460,7 +476,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         }
         int mode, arg;
         while (true) {
-          schedule_pick(env, role, num_fa, total_op, owner_words, local_owned, &mode, &arg);
+          schedule_pick(env, role, num_fa, total_op, owner_words, local_owned, &pending_ticket,
+                        &mode, &arg);
           if (mode != MODE_IDLE) break;
           const int o = k ^ 1;
           if (occupied[o] && mbar_try_wait(smem_u32(&bars.task_empty[o]), te_par[o])) {
@@ -679,8 +696,22 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t s_par = 0, o_par = 0, acc_par[2] = {0, 0};
     MA_TRACE_DECL(2 + (warp - 4))
+#ifdef MA_TRACE
+    long long acct[4] = {0, 0, 0, 0};   // idle, FA, O_proj, AR cycles of this CTA
+    int acct_n[4] = {0, 0, 0, 0};
+    long long t_mark = clock64();
+    int tl_n = 0;
+    uint32_t* tl = p.status + 8 + 11 * 2048 + 148 * 8 + blockIdx.x * 128;
+#endif
     while (true) {
       MA_NEXT_TASK(d, mode)
+#ifdef MA_TRACE
+      { const long long now = clock64(); acct[0] += now - t_mark; t_mark = now; }
+      if (warp == 4 && lane == 0 && tl_n < 31) {
+        tl[tl_n * 4 + 0] = static_cast<uint32_t>(globaltimer_ns());
+        tl[tl_n * 4 + 2] = mode; tl[tl_n * 4 + 3] = d[T_FT] * 1000 + (mode == MODE_FA ? d[TF_NBLK] : d[TO_BASE]);
+      }
+#endif
       if (lane == 0) { MA_EV(1000 + mode) }
       if (mode == MODE_FA && wg < d[TF_NT]) {
         // -------------------------------------------- softmax + epilogue of tile `wg`
@@ -884,10 +915,20 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         __threadfence_system();
       }
       __syncwarp();
+#ifdef MA_TRACE
+      { const long long now = clock64(); acct[mode] += now - t_mark; acct_n[mode]++; t_mark = now; }
+      if (warp == 4 && lane == 0 && tl_n < 31) { tl[tl_n * 4 + 1] = static_cast<uint32_t>(globaltimer_ns()); ++tl_n; }
+#endif
       if (lane == 0) mbar_arrive(smem_u32(&bars.task_empty[slot_k]));
       ++n_arrived[slot_k];
       prev_mode = mode; prev_k = slot_k; slot_k ^= 1;
     }
+#ifdef MA_TRACE
+    if (warp == 4 && lane == 0) {
+      uint32_t* ab = p.status + 8 + 11 * 2048 + blockIdx.x * 8;
+      for (int i = 0; i < 4; ++i) { ab[i] = static_cast<uint32_t>(acct[i]); ab[4 + i] = acct_n[i]; }
+    }
+#endif
   }
 #undef MA_NEXT_TASK
 #undef MA_DRAIN_IF_SWITCH

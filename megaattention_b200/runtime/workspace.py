@@ -29,7 +29,7 @@ from ..metadata.row_desc import active_counts, oproj_task_counts
 
 NUM_CTRL = 8
 NUM_SYNC = 3
-NUM_STATUS = 8 + 11 * 2048     # 8 status words + room for the optional event trace
+NUM_STATUS = 8 + 11 * 2048 + 148 * 8 + 148 * 128     # 8 status words + room for the optional event trace
 
 
 def claim_order(meta) -> np.ndarray:
