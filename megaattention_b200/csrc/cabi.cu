@@ -16,12 +16,13 @@ cudaError_t launch_fused_prefill(const CUtensorMap* maps, const KParams& kp, int
 cudaError_t fused_prefill_attributes(cudaFuncAttributes* out);
 int encode_path_maps(CUtensorMap* maps, uint64_t Q, uint64_t K, uint64_t V, uint64_t oscr,
                      uint64_t W, uint64_t H, uint64_t Hkv, uint64_t tot_q, uint64_t tot_k,
-                     uint64_t row_tiles, uint64_t w_width);
+                     uint64_t row_tiles, uint64_t w_width, uint64_t csym, uint64_t hidden,
+                     uint64_t csym_pitch);
 }  // namespace ma
 
 struct ma_plan {
   ma::KParams kp;
-  CUtensorMap maps[5];   // Q, K, V, O_scratch (2-D), W_o
+  CUtensorMap maps[6];   // Q, K, V, O_scratch (2-D), W_o, C_sym (store)
   int device;
   int num_sms;
 };
@@ -76,7 +77,8 @@ int cdiv(int a, int b) { return (a + b - 1) / b; }
 // {64, 64, 4} is a 64-k slab of 256 output columns, panel after panel.
 int ma::encode_path_maps(CUtensorMap* maps, uint64_t Q, uint64_t K, uint64_t V, uint64_t oscr,
                          uint64_t W, uint64_t H, uint64_t Hkv, uint64_t tot_q, uint64_t tot_k,
-                         uint64_t row_tiles, uint64_t w_width) {
+                         uint64_t row_tiles, uint64_t w_width, uint64_t csym, uint64_t hidden,
+                         uint64_t csym_pitch) {
   if (w_width % 64) return MA_ERR_INVALID;
   const uint64_t KL = H * 128;
   int rc;
@@ -104,6 +106,14 @@ int ma::encode_path_maps(CUtensorMap* maps, uint64_t Q, uint64_t K, uint64_t V, 
     const uint64_t str[2] = {w_width * 2, 128};
     const uint32_t box[3] = {64, 64, 4};
     rc = encode(&maps[4], W, 3, dims, str, box);
+  }
+  if (rc == MA_OK) {
+    // output tiles are stored through TMA: [rows, hidden] with the padded row pitch, so a
+    // store is clipped at `hidden` and padding columns are never written
+    const uint64_t dims[2] = {hidden, row_tiles * 128};
+    const uint64_t str[1] = {csym_pitch * 2};
+    const uint32_t box[2] = {64, 128};
+    rc = encode(&maps[5], csym, 2, dims, str, box);
   }
   return rc;
 }
@@ -226,7 +236,8 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   int rc = ma::encode_path_maps(pl->maps, d->Q, d->K, d->V, d->o_scratch, d->W_o, H, Hkv,
                                 static_cast<uint64_t>(d->max_tot_q),
                                 static_cast<uint64_t>(d->max_tot_k),
-                                static_cast<uint64_t>(d->max_row_tiles), hidden_pad);
+                                static_cast<uint64_t>(d->max_row_tiles), hidden_pad, d->csym,
+                                static_cast<uint64_t>(d->hidden), hidden_pad);
   if (rc != MA_OK) { delete pl; return rc; }
   *out = pl;
   return MA_OK;

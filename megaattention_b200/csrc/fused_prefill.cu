@@ -34,6 +34,7 @@ constexpr uint32_t kPanel = 16384;         // 128 rows x 64 bf16 (one 128-byte-s
 constexpr uint32_t kSmQ = 0;               // two Q tiles
 constexpr uint32_t kSmKV = 2 * kTile;      // ring of five K/V tiles
 constexpr int kKvSlots = 5;
+constexpr uint32_t kSmOpStaging = 4 * (16384 + 32768);   // O_proj output staging, 2 x 16 KB
 constexpr uint32_t kOpStage = 16384 + 32768;   // O_proj stage: A 128x64 + W 64x256 (4 stages)
 constexpr uint32_t kWPanel = 8192;         // 64 k-rows x 64 n bf16
 constexpr uint32_t kTmemS = 0;             // S0 at 0, S1 at 128 (P aliases the first 64 cols)
@@ -47,7 +48,7 @@ struct Bars {
   uint64_t task_empty[2];   // roles -> scheduler: task in slot k is finished   (count 11)
   uint64_t loads_done[2];   // producer: every load of the task in slot k is issued (count 1)
   uint64_t q_full[2];       // TMA: Q tile i landed
-  uint64_t q_empty[2];      // MMA: last Q K^T of the task for tile i completed
+  uint64_t q_empty[2];      // MMA: last Q K^T of tile i done + epilogue: staging released (count 2)
   uint64_t kv_full[kKvSlots];
   uint64_t kv_empty[kKvSlots];   // both MMA issuers release a slot (count 2)
   uint64_t s_full[2];       // MMA: S_i ready
@@ -329,6 +330,24 @@ __device__ __forceinline__ void issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint3
            (acc || kk > 0) ? 1u : 0u);
 }
 
+// Convert 32 fp32 values (columns col0..col0+31 of this thread's row, col0 in {0, 32}) to
+// bf16 and put them into a [128 rows][64 columns] staging panel laid out as TMA expects
+// for a 128-byte-swizzled box: 16-byte chunk c of row r lives at chunk c ^ (r & 7).
+__device__ __forceinline__ void stage_row32(uint32_t panel, int row, int col0,
+                                            const uint32_t (&v)[32], float scale) {
+  const uint32_t rbase = panel + static_cast<uint32_t>(row) * 128u;
+  const uint32_t sw = static_cast<uint32_t>(row & 7);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t c = static_cast<uint32_t>((col0 >> 3) + q);
+    st_shared_v4(rbase + ((c ^ sw) << 4),
+                 pack_bf16x2(__uint_as_float(v[8 * q + 0]) * scale, __uint_as_float(v[8 * q + 1]) * scale),
+                 pack_bf16x2(__uint_as_float(v[8 * q + 2]) * scale, __uint_as_float(v[8 * q + 3]) * scale),
+                 pack_bf16x2(__uint_as_float(v[8 * q + 4]) * scale, __uint_as_float(v[8 * q + 5]) * scale),
+                 pack_bf16x2(__uint_as_float(v[8 * q + 6]) * scale, __uint_as_float(v[8 * q + 7]) * scale));
+  }
+}
+
 }  // namespace
 
 // Task descriptor words written by the scheduler (shared memory, two slots).
@@ -345,6 +364,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
                      const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmO,
                      const __grid_constant__ CUtensorMap tmW,
+                     const __grid_constant__ CUtensorMap tmC,
                      const __grid_constant__ KParams p) {
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) Bars bars;
@@ -367,7 +387,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       mbar_init(smem_u32(&bars.task_empty[i]), 11);
       mbar_init(smem_u32(&bars.loads_done[i]), 1);
       mbar_init(smem_u32(&bars.q_full[i]), 1);
-      mbar_init(smem_u32(&bars.q_empty[i]), 1);
+      mbar_init(smem_u32(&bars.q_empty[i]), 2);
       mbar_init(smem_u32(&bars.s_full[i]), 1);
       mbar_init(smem_u32(&bars.p_full[i]), 128);
       mbar_init(smem_u32(&bars.o_done[i]), 1);
@@ -387,7 +407,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     fence_mbar_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-    tma_prefetch_desc(&tmO); tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmO); tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&s_tmem), 512);
@@ -811,36 +831,39 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         if (lane == 0) { MA_EV(35) }
         tc_fence_after();
         const float inv = (row < valid_m && l_run > 0.f) ? (1.f / l_run) : 0.f;
-        uint16_t* dst = p.o_scratch + (static_cast<size_t>(ft * 128 + row) * p.H + head) * 128;
+        // O / l -> bf16 -> this tile's Q buffer (free: every Q K^T of the task is done),
+        // then two TMA stores of 128 rows x 64 columns into O_scratch[ft, :, head, :].
+        const uint32_t stg = smem0 + kSmQ + wg * kTile;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           uint32_t o[2][32];
           tmem_ld32(t_o + hh * 64, o[0]);
           tmem_ld32(t_o + hh * 64 + 32, o[1]);
           tc_wait_ld();
-          if (hh == 1) {            // all of O_i is in registers: the next task may overwrite it
+          if (hh == 1) {            // all of O is in registers: the next task may overwrite it
             tc_fence_before();
             mbar_arrive(smem_u32(&bars.o_free[wg]));
           }
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst + hh * 64 + c * 32);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(o[c][8 * q + 0]) * inv, __uint_as_float(o[c][8 * q + 1]) * inv);
-              v.y = pack_bf16x2(__uint_as_float(o[c][8 * q + 2]) * inv, __uint_as_float(o[c][8 * q + 3]) * inv);
-              v.z = pack_bf16x2(__uint_as_float(o[c][8 * q + 4]) * inv, __uint_as_float(o[c][8 * q + 5]) * inv);
-              v.w = pack_bf16x2(__uint_as_float(o[c][8 * q + 6]) * inv, __uint_as_float(o[c][8 * q + 7]) * inv);
-              d4[q] = v;
-            }
-          }
+          stage_row32(stg + hh * kPanel, row, 0, o[0], inv);
+          stage_row32(stg + hh * kPanel, row, 32, o[1], inv);
         }
-        __threadfence();
-        fence_proxy_async_global();   // O_scratch is read back by TMA (async proxy)
+        fence_proxy_async_smem();
+        named_bar_sync(1 + wg, 128);
+        if ((warp & 3) == 0 && lane == 0) {
+          tma_store_2d(&tmO, stg, head * 128, ft * 128);
+          tma_store_2d(&tmO, stg + kPanel, head * 128 + 64, ft * 128);
+          tma_store_commit();
+          tma_store_wait_read();
+          mbar_arrive(smem_u32(&bars.q_empty[wg]));     // the producer may refill this Q buffer
+          tma_store_wait_all();
+          fence_proxy_async_all();     // O_scratch is read back by TMA loads of other CTAs
+          __threadfence();
+        }
         if (lane == 0) { MA_EV(36) }
       } else if (mode == MODE_OPROJ) {
         const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT], valid_m = d[TO_VALID];
+        const bool leader = ((warp & 3) == 0 && lane == 0);
+        const uint32_t stg = smem0 + kSmOpStaging + wg * kPanel;   // [128 rows][64 cols] bf16
         for (int h = 0; h * 2 < vnt; ++h) {
           wait_bar(env, smem_u32(&bars.acc_full[h]), acc_par[h], 0xB0 + h);
           acc_par[h] ^= 1u;
@@ -849,7 +872,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           const int o_t = 2 * h + wg;                   // column tile inside the super-group
           if (o_t < vnt) {
             const int out_n = base_out + o_t;
-            uint16_t* dst = p.csym + ((static_cast<size_t>(ft * 128 + row) * p.num_out + out_n) * 128);
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
               uint32_t r[2][32];
@@ -860,10 +882,24 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
                 tc_fence_before();
                 mbar_arrive(smem_u32(&bars.acc_free[h]));
               }
+              if (valid_m == 128) {
+                // full row tile: stage 64 columns, one TMA store (clipped at `hidden`)
+                if (leader) tma_store_wait_read();
+                named_bar_sync(1 + wg, 128);
+                stage_row32(stg, row, 0, r[0], 1.f);
+                stage_row32(stg, row, 32, r[1], 1.f);
+                fence_proxy_async_smem();
+                named_bar_sync(1 + wg, 128);
+                if (leader) {
+                  tma_store_2d(&tmC, stg, out_n * 128 + hh * 64, ft * 128);
+                  tma_store_commit();
+                }
+              } else if (row < valid_m) {
+                // last tile of a sequence: rows past valid_m must stay untouched
+                uint16_t* dst = p.csym + ((static_cast<size_t>(ft * 128 + row) * p.num_out + out_n) * 128);
 #pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                const int col0 = out_n * 128 + hh * 64 + c * 32;
-                if (row < valid_m) {
+                for (int c = 0; c < 2; ++c) {
+                  const int col0 = out_n * 128 + hh * 64 + c * 32;
                   if (col0 + 32 <= p.hidden) {
                     uint4* d4 = reinterpret_cast<uint4*>(dst + hh * 64 + c * 32);
 #pragma unroll
@@ -889,6 +925,10 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             tc_fence_before();
             mbar_arrive(smem_u32(&bars.acc_free[h]));
           }
+        }
+        if (leader) {
+          tma_store_wait_all();
+          fence_proxy_async_all();
         }
         if (p.tp > 1) __threadfence_system(); else __threadfence();
         if (lane == 0) { MA_EV(52) }
@@ -972,7 +1012,7 @@ cudaError_t launch_fused_prefill(const CUtensorMap* maps, const KParams& kp, int
     attr_set[dev] = true;
   }
   fused_prefill_kernel<<<num_ctas, kThreads, kSmemDynamic, stream>>>(maps[0], maps[1], maps[2],
-                                                                     maps[3], maps[4], kp);
+                                                                     maps[3], maps[4], maps[5], kp);
   return cudaGetLastError();
 }
 

@@ -15,7 +15,8 @@ cudaError_t launch_fused_prefill(const CUtensorMap* maps, const KParams& kp, int
                                  cudaStream_t stream);
 int encode_path_maps(CUtensorMap* maps, uint64_t Q, uint64_t K, uint64_t V, uint64_t oscr,
                      uint64_t W, uint64_t H, uint64_t Hkv, uint64_t tot_q, uint64_t tot_k,
-                     uint64_t row_tiles, uint64_t w_width);
+                     uint64_t row_tiles, uint64_t w_width, uint64_t csym, uint64_t hidden,
+                     uint64_t csym_pitch);
 }  // namespace ma
 
 namespace {
@@ -155,12 +156,13 @@ extern "C" int ma_fused_prefill_noalloc(const ma_noalloc_args* a, void* stream_)
   k.oproj_queue = reinterpret_cast<uint32_t*>(scr + kOffQueue);
 
   // ---- TMA descriptors over the caller's tensors and the scratch (host-side encoding)
-  CUtensorMap maps[5];
+  CUtensorMap maps[6];
   // W_o is read in 64-column panels straight from the caller's tensor: hidden % 64 == 0
   rc = ma::encode_path_maps(maps, a->Q, a->K, a->V, reinterpret_cast<uint64_t>(k.o_scratch), a->W_o,
                             static_cast<uint64_t>(a->H_local), static_cast<uint64_t>(a->H_kv),
                             static_cast<uint64_t>(tq), static_cast<uint64_t>(tk),
-                            static_cast<uint64_t>(R), static_cast<uint64_t>(a->hidden));
+                            static_cast<uint64_t>(R), static_cast<uint64_t>(a->hidden), a->out,
+                            static_cast<uint64_t>(a->hidden), static_cast<uint64_t>(num_out) * 128);
   if (rc != MA_OK) return rc;
 
   int n = a->num_ctas > 0 ? a->num_ctas : sms;
