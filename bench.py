@@ -172,9 +172,13 @@ def main():
     ap.add_argument("--no-unfused", action="store_true")
     ap.add_argument("--w", type=str, default=None, help="w_fa,w_oproj,w_ar override")
     ap.add_argument("--ctas", type=int, default=0)
-    ap.add_argument("--stage", default="fused", choices=["fused", "fa"],
-                    help="fa: time the attention stage alone (profiling aid)")
+    ap.add_argument("--stage", default="fused", choices=["fused", "fa", "ar"],
+                    help="fa / ar: time the attention / AllReduce stage alone (profiling aid)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--per-rank-heads", type=int, default=0,
+                    help="experiment: every rank gets this many q heads (1 kv head), c3 sequences")
+    ap.add_argument("--flags", type=int, default=None,
+                    help="launch flags (2: drain downstream work first, 4: row-tile claim order)")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -182,6 +186,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     tp = args.tp or max(world, 1)
     wl = WORKLOADS[args.workload or ("c2" if tp == 1 else "c3")]
+    if args.per_rank_heads:
+        from megaattention_b200.workloads import Workload
+        wl = Workload(f"{wl.name}-h{args.per_rank_heads}", wl.seqlens_q, args.per_rank_heads * tp, tp,
+                      wl.hidden, [tp], kv_mult=wl.kv_mult, per_rank_seed=True)
     if args.impl == "reference":
         if args.steps > 3:
             args.steps = 3
@@ -217,6 +225,8 @@ def main():
     ws.compile(w_fa=w[0], w_oproj=w[1], w_ar=w[2], num_ctas=args.ctas or None)
     ws.set_layer(meta, Qh, Kh, Vh, Wh)
     torch.cuda.synchronize()
+    if args.flags is not None:
+        ws.default_flags = args.flags
 
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)   # 4 x L2
     stream = torch.cuda.current_stream()
@@ -248,7 +258,9 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    ms_fused = timed(ws.launch if args.stage == "fused" else ws.launch_fa_only, K, W)
+    stage_fn = {"fused": ws.launch, "fa": ws.launch_fa_only,
+                "ar": lambda: ws.launch_ar_only((args.flags or 0) & ~0xF)}[args.stage]
+    ms_fused = timed(stage_fn, K, W)
     clocks = sampler.stop() if sampler else None
     ws.check_status()
 
@@ -314,10 +326,14 @@ def main():
             Ys = symm_mem.empty(wl.tot_q, wl.hidden, dtype=torch.bfloat16, device=dev)
             symm_mem.rendezvous(Ys, group)
             Ys.zero_()
-            ms_ar = timed(lambda: torch.ops.symm_mem.multimem_all_reduce_(Ys, "sum", group),
-                          max(3, K // 2), 3)
+            ms_ar_nvls = timed(lambda: torch.ops.symm_mem.multimem_all_reduce_(Ys, "sum", group),
+                               max(3, K // 2), 3)
+            ms_ar_nccl = timed(lambda: dist.all_reduce(Y), max(3, K // 2), 3)
+            ms_ar = min(ms_ar_nvls, ms_ar_nccl)
         serial = ms_fa + ms_gemm + ms_ar
-        unfused = {"fa_ms": ms_fa, "oproj_cublas_ms": ms_gemm, "allreduce_nvls_ms": ms_ar,
+        unfused = {"fa_ms": ms_fa, "oproj_cublas_ms": ms_gemm, "allreduce_ms": ms_ar,
+                   "allreduce_symm_mem_multimem_ms": ms_ar_nvls if world > 1 else 0.0,
+                   "allreduce_nccl_ms": ms_ar_nccl if world > 1 else 0.0,
                    "serial_ms": serial, "ideal_ms": max(ms_fa + ms_gemm, ms_ar),
                    "ratio_serial_over_fused": serial / ms_fused,
                    "fa": "this library's attention stage alone (MA_FLAG_FA_ONLY)"}

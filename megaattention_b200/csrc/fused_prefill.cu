@@ -148,30 +148,51 @@ __device__ __forceinline__ bool try_pop_oproj(const KParams& p, int total_op, in
   return true;
 }
 
-__device__ __forceinline__ bool try_claim_ar(const KParams& p, int owner_words, int local_owned,
+// Claim one ready AllReduce slot of this (owner) rank.
+//
+// The reference has the last of the tp arriving ranks set a bit in the owner's ready
+// bitset, found by its atomic add returning tp-1, and owners claim by clearing the lowest
+// set bit (fused_fa_oproj_ar.py:192-239, 294-317).  On NVSwitch that costs every O_proj
+// task a blocking remote round trip (tens of microseconds once the links carry the
+// AllReduce itself) and makes all polling CTAs fight for one bit.  Here arrivals are
+// fire-and-forget adds on the owner's ready_count; a slot is ready when its count equals
+// tp, and the owner's CTAs each watch their own stretch of the count array (plus a few
+// neighbours', and now and then all of it), claiming with a compare-and-swap that marks the
+// count.  ready_bits is no longer used.
+constexpr uint32_t kArClaimed = 0x40000000u;
+__device__ __forceinline__ bool try_claim_ar(const KParams& p, int local_owned, uint32_t poll_no,
                                              int* arg) {
-  if (owner_words <= 0) return false;
-  const uint32_t start = ld_relaxed_gpu(p.ctrl + C_AR_CURSOR);
-  for (int i = 0; i < owner_words; ++i) {
-    const uint32_t w = (start + i) % static_cast<uint32_t>(owner_words);
-    uint64_t* wp = reinterpret_cast<uint64_t*>(p.ready_bits) + w;
-    const uint64_t word = ld_acquire_sys_u64(wp);
-    if (word == 0) continue;
-    const uint64_t lowest = word & (0ull - word);
-    const int bit = __ffsll(static_cast<long long>(lowest)) - 1;
-    const uint64_t old = atom_and_acqrel_sys_u64(wp, ~lowest);
-    if ((old & lowest) == 0) continue;          // another CTA cleared it first
-    const int owner_idx = static_cast<int>(w) * 64 + bit;
-    if (owner_idx >= local_owned) continue;     // stray tail bit: cleared, not counted
-    atom_exch_relaxed_gpu(p.ctrl + C_AR_CURSOR, w);
-    *arg = owner_idx * p.tp + p.rank;
-    return true;
+  const int n = local_owned;
+  if (n <= 0) return false;
+  const int per = (n + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int base = static_cast<int>((static_cast<long long>(blockIdx.x) * per) % n);
+  int span = ((poll_no & 7u) == 7u) ? n : per * 4 + 8;
+  if (span > n) span = n;
+  const uint32_t want = static_cast<uint32_t>(p.tp);
+  for (int j0 = 0; j0 < span; j0 += 8) {
+    uint32_t c[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      int idx = base + j0 + u;
+      if (idx >= n) idx -= n;
+      c[u] = (j0 + u < span) ? ld_relaxed_sys(p.ready_count + idx) : 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (c[u] != want) continue;
+      int idx = base + j0 + u;
+      if (idx >= n) idx -= n;
+      if (atom_cas_acqrel_sys(p.ready_count + idx, want, want | kArClaimed) == want) {
+        *arg = idx * p.tp + p.rank;
+        return true;
+      }
+    }
   }
   return false;
 }
 
 __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, int total_op,
-                                           int owner_words, int local_owned, int* pending,
+                                           int local_owned, uint32_t poll_no, int* pending,
                                            int* mode, int* arg) {
   const KParams& p = *e.p;
   *mode = MODE_IDLE;
@@ -181,24 +202,42 @@ __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, i
     *mode = MODE_DONE;
     return;
   }
+  if (p.flags & 8u) {
+    // AllReduce-only launch: every owned slot is taken as ready (the caller made sure all
+    // ranks' partials are in place); slots are handed out by a counter
+    if (static_cast<int>(ld_acquire_gpu(p.ctrl + C_AR_DONE)) >= local_owned) { *mode = MODE_DONE; return; }
+    if (static_cast<int>(ld_relaxed_gpu(p.ctrl + C_AR_CURSOR)) < local_owned) {
+      const int idx = static_cast<int>(atom_add_relaxed_gpu(p.ctrl + C_AR_CURSOR, 1u));
+      if (idx < local_owned) { *mode = MODE_AR; *arg = idx * p.tp + p.rank; }
+    }
+    return;
+  }
   const bool fa_only = (p.flags & 1u) != 0;
   const int fa_d = static_cast<int>(ld_acquire_gpu(p.ctrl + C_FA_DONE));
   bool done = fa_d >= num_fa;
   if (!fa_only) {
     const int op_d = static_cast<int>(ld_acquire_gpu(p.ctrl + C_OP_DONE));
     const int ar_d = static_cast<int>(ld_acquire_gpu(p.ctrl + C_AR_DONE));
-    done = done && op_d >= total_op && ar_d >= local_owned;
+    done = done && op_d >= total_op && ((p.flags & 16u) || ar_d >= local_owned);
   }
   if (done) { *mode = MODE_DONE; return; }
-  // probe order by role: 0: FA,OPROJ,AR  1: OPROJ,AR,FA  2: AR,FA,OPROJ
+  // probe order by role: 0: FA,OPROJ,AR  1: OPROJ,AR,FA  2: AR,FA,OPROJ (the reference's
+  // three orders).  With the "drain first" launch flag downstream work goes first so that
+  // AllReduce traffic starts early and keeps flowing: roles 0/1 become 3: OPROJ,FA,AR and
+  // role 2 becomes 4: AR,OPROJ,FA.
   for (int i = 0; i < 3; ++i) {
-    const int src = (role == 0) ? (MODE_FA + i) : (role == 1) ? (MODE_OPROJ + i) : (MODE_AR + i);
-    const int m = (src > MODE_AR) ? src - 3 : src;
+    int m;
+    if (role == 3) m = (i == 0) ? MODE_OPROJ : (i == 1) ? MODE_FA : MODE_AR;
+    else if (role == 4) m = MODE_AR - i;
+    else {
+      const int src = (role == 0) ? (MODE_FA + i) : (role == 1) ? (MODE_OPROJ + i) : (MODE_AR + i);
+      m = (src > MODE_AR) ? src - 3 : src;
+    }
     bool ok = false;
     if (m == MODE_FA) ok = try_fa(p, num_fa, arg);
     else if (fa_only) ok = false;
     else if (m == MODE_OPROJ) ok = try_pop_oproj(p, total_op, pending, arg);
-    else if (p.tp > 1) ok = try_claim_ar(p, owner_words, local_owned, arg);
+    else if (p.tp > 1 && !(p.flags & 16u)) ok = try_claim_ar(p, local_owned, poll_no, arg);
     if (ok) { *mode = m; return; }
   }
 }
@@ -234,7 +273,9 @@ __device__ __forceinline__ void finish_ar_slot(const KParams& p, int slot) {
 
 // After an O_proj task: tell the slot's owner rank that this rank's partial is in place.
 __device__ __noinline__ void publish_ar_ready(const KParams& p, int slot) {
-  if (p.tp == 1) {
+  if (p.flags & 16u) {
+    // partial sums only (measurement aid): no AllReduce, no cross-rank traffic
+  } else if (p.tp == 1) {
     // one rank: the partial is the result; account the (identity) AllReduce right here
     fence_acq_rel_gpu();
     finish_ar_slot(p, slot);
@@ -242,12 +283,7 @@ __device__ __noinline__ void publish_ar_ready(const KParams& p, int slot) {
     fence_acq_rel_sys();
     const int owner_rank = slot % p.tp;
     const int owner_idx = slot / p.tp;
-    uint32_t* rc = reinterpret_cast<uint32_t*>(p.peer_rc[owner_rank]) + owner_idx;
-    const uint32_t old = atom_add_acqrel_sys(rc, 1u);
-    if (old + 1u == static_cast<uint32_t>(p.tp)) {
-      uint64_t* rb = reinterpret_cast<uint64_t*>(p.peer_rb[owner_rank]) + (owner_idx >> 6);
-      atom_or_release_sys_u64(rb, 1ull << (owner_idx & 63));
-    }
+    red_add_release_sys(reinterpret_cast<uint32_t*>(p.peer_rc[owner_rank]) + owner_idx, 1u);
   }
   atom_add_release_gpu(p.ctrl + C_OP_DONE, 1u);
 }
@@ -345,6 +381,30 @@ __device__ __forceinline__ void stage_row32(uint32_t panel, int row, int col0,
                  pack_bf16x2(__uint_as_float(v[8 * q + 2]) * scale, __uint_as_float(v[8 * q + 3]) * scale),
                  pack_bf16x2(__uint_as_float(v[8 * q + 4]) * scale, __uint_as_float(v[8 * q + 5]) * scale),
                  pack_bf16x2(__uint_as_float(v[8 * q + 6]) * scale, __uint_as_float(v[8 * q + 7]) * scale));
+  }
+}
+
+// One AllReduce slot: 128 rows x (vnt x 128) bf16 columns, reduced in the switch and
+// written back to every rank.  `nthr` threads cooperate; each keeps U 16-byte reductions in
+// flight before its first store (NVLink round trips are microseconds).
+template <int U>
+__device__ __forceinline__ void ar_slot(const KParams& p, int ft, int base_out, int vnt, int t,
+                                        int nthr) {
+  const int total = vnt * 2048;                    // 16-byte chunks in the slot
+  auto chunk_addr = [&](int c) -> unsigned long long {
+    const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
+    const size_t elem =
+        ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
+    return p.csym_mc + elem * 2;
+  };
+  for (int c0 = t; c0 < total; c0 += nthr * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (c0 + u * nthr < total) v[u] = multimem_ld_reduce_bf16x8(chunk_addr(c0 + u * nthr));
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (c0 + u * nthr < total) multimem_st_b128(chunk_addr(c0 + u * nthr), v[u]);
   }
 }
 
@@ -449,19 +509,20 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       // ==================================================================== scheduler
       const int num_fa = p.actv[0];
       const int total_op = p.actv[1];
-      const int owner_words = p.actv[4];
       const int local_owned = p.actv[5];
       int role;
       {
         const int wsum = p.w_fa + p.w_oproj + p.w_ar;
         const int r = static_cast<int>(blockIdx.x) % wsum;
         role = (r < p.w_fa) ? 0 : (r < p.w_fa + p.w_oproj) ? 1 : 2;
+        if (p.flags & 2u) role = (role == 2) ? 4 : 3;
       }
       int k = 0;
       bool occupied[2] = {false, false};
       uint32_t te_par[2] = {0, 0}, ld_par[2] = {0, 0};
       bool ld_pending[2] = {false, false};
       int pending_ticket = -1;
+      uint32_t poll_no = 0;
       int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0};
       auto publish = [&](int kk) {
         if (s_abort) return;
@@ -496,7 +557,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         }
         int mode, arg;
         while (true) {
-          schedule_pick(env, role, num_fa, total_op, owner_words, local_owned, &pending_ticket,
+          schedule_pick(env, role, num_fa, total_op, local_owned, poll_no++, &pending_ticket,
                         &mode, &arg);
           if (mode != MODE_IDLE) break;
           const int o = k ^ 1;
@@ -512,7 +573,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         if (mode == MODE_FA) {
           const int nt = p.pair ? 2 : 1;
           const int pos = arg / p.H, head0 = arg % p.H;
-          const int ft = p.fa_order ? p.fa_order[pos] : pos;
+          const int ft = (p.fa_order && !(p.flags & 4u)) ? p.fa_order[pos] : pos;
           const int b = p.fa_b[ft], mb = p.fa_mb[ft];
           const int q0 = p.cu_q[b], q_len = p.cu_q[b + 1] - q0;
           const int k0 = p.cu_k[b], k_len = p.cu_k[b + 1] - k0;
@@ -926,33 +987,21 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             mbar_arrive(smem_u32(&bars.acc_free[h]));
           }
         }
+        // Ordering towards other CTAs / ranks: the leader waits for its TMA stores, rows
+        // written directly get a gpu-scope fence; the one system-scope fence per task is
+        // the scheduler's, after it has seen every warp arrive.  (A system fence by each of
+        // the 256 threads costs tens of microseconds per task while NVLink is busy.)
         if (leader) {
           tma_store_wait_all();
           fence_proxy_async_all();
         }
-        if (p.tp > 1) __threadfence_system(); else __threadfence();
+        if (valid_m != 128) __threadfence();
         if (lane == 0) { MA_EV(52) }
       } else if (mode == MODE_AR) {
         const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT];
-        const int total = vnt * 2048;                    // 16-byte chunks in the slot
         const int ctid = tid - 128;
-        for (int c0 = ctid; c0 < total; c0 += 256 * 4) {
-          uint4 v[4];
-          unsigned long long a[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = c0 + u * 256;
-            const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
-            const size_t elem =
-                ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
-            a[u] = p.csym_mc + elem * 2;
-            if (c < total) v[u] = multimem_ld_reduce_bf16x8(a[u]);
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (c0 + u * 256 < total) multimem_st_b128(a[u], v[u]);
-        }
-        __threadfence_system();
+        ar_slot<16>(p, ft, base_out, vnt, ctid, 256);
+        if (lane == 0) __threadfence_system();   // one per warp; the scheduler fences again
       }
       __syncwarp();
 #ifdef MA_TRACE
@@ -989,7 +1038,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       if (blockIdx.x == 0 && tid < 8) p.ctrl[tid] = 0u;
       __threadfence();
       grid_sync(env, S_GS_CLEANDONE);
-      if (p.tp > 1 && !(p.flags & 1u)) rank_barrier(env);
+      if (p.tp > 1 && !(p.flags & (1u | 16u))) rank_barrier(env);
     }
   }
 

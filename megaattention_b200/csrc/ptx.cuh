@@ -299,6 +299,21 @@ __device__ __forceinline__ int atom_add_release_sys_s32(int* p, int v) {
                : "memory");
   return o;
 }
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// fire-and-forget add (no value comes back, so the issuing thread does not wait for NVLink)
+__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t atom_cas_acqrel_sys(uint32_t* p, uint32_t cmp, uint32_t v) {
+  uint32_t o;
+  asm volatile("atom.acq_rel.sys.global.cas.b32 %0, [%1], %2, %3;" : "=r"(o)
+               : "l"(p), "r"(cmp), "r"(v) : "memory");
+  return o;
+}
 __device__ __forceinline__ uint32_t atom_cas_relaxed_gpu(uint32_t* p, uint32_t cmp, uint32_t v) {
   uint32_t o;
   asm volatile("atom.relaxed.gpu.global.cas.b32 %0, [%1], %2, %3;" : "=r"(o)

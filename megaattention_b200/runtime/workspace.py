@@ -51,6 +51,7 @@ class FusedFaOprojArWorkspace:
         self._plan = None
         self._args = None
         self._meta = None
+        self.default_flags = 0   # OR of _cabi.MA_FLAG_* applied by launch()
 
     # ------------------------------------------------------------------ create
     @classmethod
@@ -245,8 +246,9 @@ class FusedFaOprojArWorkspace:
     def _stream(self):
         return getattr(self, "_ts", None) or torch.cuda.current_stream(self.dev)
 
-    def launch(self, flags=0):
+    def launch(self, flags=None):
         assert self._plan is not None, "call compile() first"
+        flags = self.default_flags if flags is None else flags
         args = _cabi.LaunchArgs(self._args.w_fa, self._args.w_oproj, self._args.w_ar,
                                 self._args.num_ctas, int(flags))
         _cabi.check(_cabi.lib.ma_launch(self._plan, C.byref(args),
@@ -255,6 +257,11 @@ class FusedFaOprojArWorkspace:
     def launch_fa_only(self):
         """Attention stage alone (fills ``Oscr``); used by the unfused baseline."""
         self.launch(flags=_cabi.MA_FLAG_FA_ONLY)
+
+    def launch_ar_only(self, extra_flags=0):
+        """AllReduce stage alone over every slot of ``csym`` (tp > 1).  Every rank's partial
+        must be complete before any rank launches (e.g. after a host barrier)."""
+        self.launch(flags=_cabi.MA_FLAG_AR_ONLY | extra_flags)
 
     def check_status(self):
         """Synchronise the launch stream and raise if a device-side wait gave up."""
