@@ -32,6 +32,7 @@ import torch  # noqa: E402
 from megaattention_b200.workloads import (  # noqa: E402
     WORKLOADS, make_rank_inputs, fa_flops, oproj_flops, ar_bytes)
 from megaattention_b200.metadata import build_row_desc, choose_launch_config  # noqa: E402
+from megaattention_b200.metadata.launch_heuristic import launch_flags_b200  # noqa: E402
 
 METRIC = "fused_fa_oproj_ar_prefill_tflops"
 UNIT = "TFLOP/s"
@@ -225,8 +226,8 @@ def main():
     ws.compile(w_fa=w[0], w_oproj=w[1], w_ar=w[2], num_ctas=args.ctas or None)
     ws.set_layer(meta, Qh, Kh, Vh, Wh)
     torch.cuda.synchronize()
-    if args.flags is not None:
-        ws.default_flags = args.flags
+    ws.default_flags = (args.flags if args.flags is not None
+                        else launch_flags_b200(meta, wl.hidden, tp, h))
 
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)   # 4 x L2
     stream = torch.cuda.current_stream()
@@ -352,7 +353,7 @@ def main():
             "data": "synthetic",
             "config": {"workload": f"{wl.name} tp{tp}" + ("" if args.stage == "fused" else " (attention stage only)"), "seqlens_q": wl.seqlens_q,
                        "kv_mult": wl.kv_mult, "H_local": h, "H_kv": hkv, "hidden": wl.hidden,
-                       "role_weights": list(w), "sg": cfg.sg,
+                       "role_weights": list(w), "sg": cfg.sg, "launch_flags": ws.default_flags,
                        "l2": "512 MiB buffer written before every timed launch"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": K,
             "clocks": clocks, "unfused": unfused,

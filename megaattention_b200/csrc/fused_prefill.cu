@@ -388,7 +388,7 @@ __device__ __forceinline__ void stage_row32(uint32_t panel, int row, int col0,
 // written back to every rank.  `nthr` threads cooperate; each keeps U 16-byte reductions in
 // flight before its first store (NVLink round trips are microseconds).
 template <int U>
-__device__ __forceinline__ void ar_slot(const KParams& p, int ft, int base_out, int vnt, int t,
+__device__ __noinline__ void ar_slot(const KParams& p, int ft, int base_out, int vnt, int t,
                                         int nthr) {
   const int total = vnt * 2048;                    // 16-byte chunks in the slot
   auto chunk_addr = [&](int c) -> unsigned long long {

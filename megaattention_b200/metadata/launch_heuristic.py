@@ -66,3 +66,23 @@ def choose_launch_config_b200(meta, hidden: int, tp_size: int,
     row = _TABLE[0] if estimate_work_ratio_kv(meta, hidden, N_TILE) < _R_LO else _TABLE[1]
     sg = max(1, min(row[2], cdiv(hidden, N_TILE)))
     return LaunchConfig(w_fa=row[0], w_oproj=row[1], w_ar=int(tp_size > 1), sg=sg)
+
+
+def launch_flags_b200(meta, hidden: int, tp_size: int, H_local: int, D: int = 128) -> int:
+    """Launch flags for the sm_100a kernel (no reference counterpart).
+
+    Returns 2 ("drain first": CTAs probe O_proj before attention, AllReduce first on the
+    AllReduce-role CTAs) when the launch is expected to be NVLink bound, else 0.  The
+    estimate compares the un-padded FLOPs at an effective 1.2 PFLOP/s with the AllReduce
+    payload at the ~0.38 TB/s the in-switch reduction sustains on 8 B200s.
+    """
+    if tp_size <= 1:
+        return 0
+    lq = np.diff(meta.cu_seqlens_q.astype(np.int64)).astype(np.float64)
+    lk = np.diff(meta.cu_seqlens_k.astype(np.int64)).astype(np.float64)
+    fa = float((H_local * 2.0 * (lq * (lk - lq) + lq * (lq + 1) / 2) * (2 * D)).sum())
+    tot_q = float(lq.sum())
+    flops = fa + 2.0 * tot_q * H_local * D * hidden
+    t_compute = flops / 1.2e15
+    t_ar = tot_q * hidden * 2.0 / 0.38e12
+    return 2 if t_ar > 0.8 * t_compute else 0
