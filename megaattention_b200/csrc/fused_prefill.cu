@@ -69,7 +69,7 @@ struct Env {
 
 // Optional event trace (compiled in with -DMA_TRACE only): CTA 0 stamps (code, clock) pairs
 // per role into the words that follow the 8 status words.
-#ifdef MA_TRACE
+#ifdef MA_TRACE_FINE
 #define MA_TRACE_DECL(role_id) uint32_t tr_n = 0; const int tr_role = (role_id);
 #define MA_EV(code)                                                                        \
   if (blockIdx.x == 0 && tr_n < 1000) {                                                    \
@@ -520,7 +520,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       int k = 0;
       bool occupied[2] = {false, false};
       uint32_t te_par[2] = {0, 0}, ld_par[2] = {0, 0};
-      bool ld_pending[2] = {false, false};
+      bool ld_pending[2] = {false, false}, ld_skip[2] = {false, false};
       int pending_ticket = -1;
       uint32_t poll_no = 0;
       int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0};
@@ -554,6 +554,9 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           wait_bar(env, smem_u32(&bars.loads_done[k ^ 1]), ld_par[k ^ 1], 0x128 + k);
           ld_par[k ^ 1] ^= 1u;
           ld_pending[k ^ 1] = false;
+        } else if (ld_skip[k ^ 1]) {
+          ld_par[k ^ 1] ^= 1u;        // that task's loads_done phase is never waited for
+          ld_skip[k ^ 1] = false;
         }
         int mode, arg;
         while (true) {
@@ -600,7 +603,10 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         mbar_arrive(smem_u32(&bars.task_full[k]));
         if (mode == MODE_DONE) break;
         occupied[k] = true;
-        ld_pending[k] = true;
+        // claim-ahead is only held back behind long attention tasks; short tasks (O_proj,
+        // AllReduce, a few key blocks) want their successor posted before they end
+        ld_pending[k] = (mode == MODE_FA && d[TF_NBLK] > 6);
+        ld_skip[k] = !ld_pending[k];
         k ^= 1;
       }
     } else if (warp == 0 && lane == 0) {
