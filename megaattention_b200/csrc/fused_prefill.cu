@@ -559,10 +559,22 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           ld_skip[k ^ 1] = false;
         }
         int mode, arg;
+        uint64_t idle_t0 = 0;
         while (true) {
           schedule_pick(env, role, num_fa, total_op, local_owned, poll_no++, &pending_ticket,
                         &mode, &arg);
           if (mode != MODE_IDLE) break;
+          // nothing to do and not finished: bounded like every other wait (a rank that
+          // never shows up, or counts that can never be reached, must not hang the GPU)
+          if ((poll_no & 15u) == 0) {
+            const uint64_t now = globaltimer_ns();
+            if (idle_t0 == 0) idle_t0 = now;
+            else if (now - idle_t0 > p.wait_limit_ns) {
+              report(env, ST_TIMEOUT_IDLE, poll_no, static_cast<uint32_t>(pending_ticket));
+              mode = MODE_DONE;
+              break;
+            }
+          }
           const int o = k ^ 1;
           if (occupied[o] && mbar_try_wait(smem_u32(&bars.task_empty[o]), te_par[o])) {
             te_par[o] ^= 1u;

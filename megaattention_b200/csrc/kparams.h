@@ -16,7 +16,7 @@ enum : int { MODE_IDLE = 0, MODE_FA = 1, MODE_OPROJ = 2, MODE_AR = 3, MODE_DONE 
 // status[0] codes
 enum : uint32_t {
   ST_OK = 0, ST_TIMEOUT_MBAR = 1, ST_TIMEOUT_PUBLISH = 2, ST_TIMEOUT_GRID = 3,
-  ST_TIMEOUT_NVL = 4, ST_BAD_DESC = 5
+  ST_TIMEOUT_NVL = 4, ST_BAD_DESC = 5, ST_TIMEOUT_IDLE = 6
 };
 
 constexpr int kMaxTp = 8;

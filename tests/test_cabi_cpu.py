@@ -1,0 +1,68 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares,
+its structs have the layout the ctypes binding assumes, and argument validation that does
+not need a device answers with the documented error codes.  No kernel is launched."""
+import ctypes as C
+import os
+import re
+
+from megaattention_b200 import _cabi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "megaattn_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ma_[a-z_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    names = _declared_functions()
+    assert {"ma_query_device", "ma_plan_create", "ma_launch", "ma_read_status",
+            "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc"} <= set(names)
+    for n in names:
+        assert getattr(_cabi.lib, n) is not None, n
+    assert set(names) == set(_cabi.EXPORTS)
+
+
+def test_struct_layouts_match_the_header():
+    # sizes / offsets computed by hand from the header (8-byte alignment for uint64_t)
+    assert C.sizeof(_cabi.LaunchArgs) == 20
+    assert C.sizeof(_cabi.Status) == 16
+    assert _cabi.PlanDesc.Q.offset == 56
+    assert _cabi.PlanDesc.peer_ready_count.offset == 56 + 21 * 8
+    assert _cabi.PlanDesc.fa_order.offset == 56 + 21 * 8 + 3 * 64
+    assert C.sizeof(_cabi.PlanDesc) == 56 + 21 * 8 + 3 * 64 + 8
+    assert _cabi.NoAllocArgs.seqlens_q.offset == 40
+    assert C.sizeof(_cabi.NoAllocArgs) == 40 + 2 * 8 + 5 * 8 + 8
+
+
+def test_error_strings_and_null_arguments():
+    for code in (0, -1, -2, -3, -4, -5):
+        assert _cabi.strerror(code) not in ("", "unknown error")
+    assert _cabi.strerror(-99) == "unknown error"
+    plan = C.c_void_p()
+    assert _cabi.lib.ma_plan_create(None, C.byref(plan)) == _cabi.MA_ERR_INVALID
+    assert _cabi.lib.ma_launch(None, None, None) == _cabi.MA_ERR_INVALID
+    assert _cabi.lib.ma_read_status(None, None, None) == _cabi.MA_ERR_INVALID
+    assert _cabi.lib.ma_fused_prefill_noalloc(None, None) == _cabi.MA_ERR_INVALID
+    _cabi.lib.ma_plan_destroy(None)          # a no-op, must not crash
+
+
+def test_shape_validation_happens_before_any_device_call():
+    d = _cabi.PlanDesc()
+    d.D, d.tp_size, d.H_local, d.H_kv = 64, 1, 8, 1       # head_dim 64 is not supported
+    plan = C.c_void_p()
+    assert _cabi.lib.ma_plan_create(C.byref(d), C.byref(plan)) == _cabi.MA_ERR_INVALID
+    d.D, d.tp_size = 128, 9                                # more ranks than MA_MAX_TP
+    assert _cabi.lib.ma_plan_create(C.byref(d), C.byref(plan)) == _cabi.MA_ERR_INVALID
+    d.tp_size, d.H_local, d.H_kv = 1, 8, 3                 # q heads not a multiple of kv heads
+    assert _cabi.lib.ma_plan_create(C.byref(d), C.byref(plan)) == _cabi.MA_ERR_INVALID
+    a = _cabi.NoAllocArgs()
+    a.H_local, a.H_kv, a.hidden, a.super_group_n_tiles, a.num_batch = 8, 1, 100, 4, 1
+    q = (C.c_int32 * 1)(128)
+    a.seqlens_q = q
+    a.Q = a.K = a.V = a.W_o = a.out = 256
+    assert _cabi.lib.ma_fused_prefill_noalloc(C.byref(a), None) == _cabi.MA_ERR_INVALID
+    a.hidden, a.num_batch = 128, 513
+    assert _cabi.lib.ma_fused_prefill_noalloc(C.byref(a), None) == _cabi.MA_ERR_CAPACITY
