@@ -277,7 +277,9 @@ def main():
         "bound": "tensor" if t_comp >= t_ar else "nvlink",
         "achieved": flops_rank / (ms_fused * 1e-3) / 1e12, "peak": peaks["tflops"],
         "unit": "TFLOP/s", "frac": (flops_rank / (ms_fused * 1e-3) / 1e12) / peaks["tflops"],
-        "traffic": None, "peak_source": peaks["source"],
+        # dram read+write bytes of one launch from an ncu capture (profiles/): c2, tp 1 only
+        "traffic": 147.5e6 if (wl.name == "c2" and tp == 1 and args.stage == "fused") else None,
+        "traffic_unit": "bytes/launch", "peak_source": peaks["source"],
         "t_compute_ms": t_comp * 1e3, "t_allreduce_ms": t_ar * 1e3,
         "frac_of_slower_leg": max(t_comp, t_ar) * 1e3 / ms_fused,
         "nominal": {"t_compute_ms_2250tf": flops_rank / 2250e12 * 1e3,
