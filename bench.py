@@ -173,7 +173,7 @@ def main():
     ap.add_argument("--no-unfused", action="store_true")
     ap.add_argument("--w", type=str, default=None, help="w_fa,w_oproj,w_ar override")
     ap.add_argument("--ctas", type=int, default=0)
-    ap.add_argument("--stage", default="fused", choices=["fused", "fa", "ar"],
+    ap.add_argument("--stage", default="fused", choices=["fused", "fa", "ar", "oproj"],
                     help="fa / ar: time the attention / AllReduce stage alone (profiling aid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--per-rank-heads", type=int, default=0,
@@ -260,7 +260,8 @@ def main():
     if sampler:
         sampler.start()
     stage_fn = {"fused": ws.launch, "fa": ws.launch_fa_only,
-                "ar": lambda: ws.launch_ar_only((args.flags or 0) & ~0xF)}[args.stage]
+                "ar": lambda: ws.launch_ar_only((args.flags or 0) & ~0xF),
+                "oproj": ws.launch_oproj_only}[args.stage]
     ms_fused = timed(stage_fn, K, W)
     clocks = sampler.stop() if sampler else None
     ws.check_status()

@@ -43,6 +43,7 @@ typedef enum ma_error {
 #define MA_FLAG_AR_ONLY 8u    /* AllReduce stage only: every owned slot of C_sym is reduced;
                                  all ranks' partials must already be in place             */
 #define MA_FLAG_NO_AR 16u     /* stop after O_proj: C_sym holds this rank's partial (measurement aid) */
+#define MA_FLAG_OPROJ_ONLY 32u /* O_proj stage only (single rank): O_scratch must be complete */
 #define MA_FLAG_TILE_ORDER 4u /* claim attention tasks in row-tile order, ignoring fa_order */
 
 typedef struct ma_devinfo {

@@ -15,6 +15,8 @@ MA_FLAG_FA_ONLY = 1
 MA_FLAG_DRAIN_FIRST = 2
 MA_FLAG_TILE_ORDER = 4
 MA_FLAG_AR_ONLY = 8
+MA_FLAG_NO_AR = 16
+MA_FLAG_OPROJ_ONLY = 32
 
 MA_OK = 0
 MA_ERR_INVALID = -1

@@ -52,13 +52,13 @@ struct Bars {
   uint64_t kv_full[kKvSlots];
   uint64_t kv_empty[kKvSlots];   // both MMA issuers release a slot (count 2)
   uint64_t s_full[2];       // MMA: S_i ready
-  uint64_t p_full[2];       // softmax threads: P_i written (count 128)
+  uint64_t p_full[2];       // softmax warps: P_i written (count 4, one arrival per warp)
   uint64_t o_done[2];       // MMA: last P V of the task for tile i completed
-  uint64_t o_free[2];       // epilogue threads: O_i read out (count 128)
+  uint64_t o_free[2];       // epilogue warps: O_i read out (count 4)
   uint64_t op_full[4];
   uint64_t op_empty[4];
   uint64_t acc_full[2];     // MMA: O_proj accumulator half h complete
-  uint64_t acc_free[2];     // epilogue threads: half h read out (count 256)
+  uint64_t acc_free[2];     // epilogue warps: half h read out (count 8)
   uint64_t dbg;             // trace builds only
 };
 
@@ -209,6 +209,26 @@ __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, i
     if (static_cast<int>(ld_relaxed_gpu(p.ctrl + C_AR_CURSOR)) < local_owned) {
       const int idx = static_cast<int>(atom_add_relaxed_gpu(p.ctrl + C_AR_CURSOR, 1u));
       if (idx < local_owned) { *mode = MODE_AR; *arg = idx * p.tp + p.rank; }
+    }
+    return;
+  }
+  if (p.flags & 32u) {
+    // O_proj-only launch (single rank): O_scratch is taken as complete, slots are handed
+    // out in order by the consume counter
+    if (static_cast<int>(ld_acquire_gpu(p.ctrl + C_OP_DONE)) >= total_op) { *mode = MODE_DONE; return; }
+    if (static_cast<int>(ld_relaxed_gpu(p.ctrl + C_OP_CONSUME)) < total_op) {
+      const int t = static_cast<int>(atom_add_relaxed_gpu(p.ctrl + C_OP_CONSUME, 1u));
+      if (t < total_op) { *mode = MODE_OPROJ; *arg = t; }
+    }
+    return;
+  }
+  if (p.flags & 32u) {
+    // O_proj-only launch (single rank): O_scratch is taken as complete, slots are handed
+    // out in order by the consume counter
+    if (static_cast<int>(ld_acquire_gpu(p.ctrl + C_OP_DONE)) >= total_op) { *mode = MODE_DONE; return; }
+    if (static_cast<int>(ld_relaxed_gpu(p.ctrl + C_OP_CONSUME)) < total_op) {
+      const int t = static_cast<int>(atom_add_relaxed_gpu(p.ctrl + C_OP_CONSUME, 1u));
+      if (t < total_op) { *mode = MODE_OPROJ; *arg = t; }
     }
     return;
   }
@@ -449,11 +469,11 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       mbar_init(smem_u32(&bars.q_full[i]), 1);
       mbar_init(smem_u32(&bars.q_empty[i]), 2);
       mbar_init(smem_u32(&bars.s_full[i]), 1);
-      mbar_init(smem_u32(&bars.p_full[i]), 128);
+      mbar_init(smem_u32(&bars.p_full[i]), 4);
       mbar_init(smem_u32(&bars.o_done[i]), 1);
-      mbar_init(smem_u32(&bars.o_free[i]), 128);
+      mbar_init(smem_u32(&bars.o_free[i]), 4);
       mbar_init(smem_u32(&bars.acc_full[i]), 1);
-      mbar_init(smem_u32(&bars.acc_free[i]), 256);
+      mbar_init(smem_u32(&bars.acc_free[i]), 8);
     }
     for (int i = 0; i < kKvSlots; ++i) {
       mbar_init(smem_u32(&bars.kv_full[i]), 1);
@@ -662,6 +682,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
               const uint32_t a_dst = smem0 + st * kOpStage;
               // A chunk 128 x 64 and a W slab of 64 k x 256 n (4 panels; panels past the
               // padded width are filled with zeros)
+              MA_EV(62)
               mbar_expect_tx(bar, kPanel + 4u * kWPanel);
               tma_load_2d(a_dst, &tmO, bar, kc * 64, ft * 128);
               tma_load_3d(a_dst + kPanel, &tmW, bar, 0, kc * 64, (base_out + 2 * h) * 2);
@@ -762,8 +783,10 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           for (int h = 0; h * 2 < vnt; ++h) {
             const int ncols = min(2, vnt - 2 * h) * 128;
             const uint32_t idesc = make_idesc_bf16(128, ncols, 0, 1);
+            MA_EV(42)
             wait_bar(env, smem_u32(&bars.acc_free[h]), (acc_uses[h] & 1u) ^ 1u, 0xA8 + h);
             ++acc_uses[h];
+            MA_EV(43)
             for (int kc = 0; kc < nkc; ++kc) {
               const uint32_t st = opc & 3u;
               wait_bar(env, smem_u32(&bars.op_full[st]), (opc >> 2) & 1u, 0xA0 + st);
@@ -847,9 +870,10 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           }
           float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int kx = 0; kx < 32; ++kx)
+          for (int kx = 0; kx < 32; kx += 2)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) mx[c] = fmaxf(mx[c], __uint_as_float(s[c][kx]));
+            for (int c = 0; c < 4; ++c)
+              mx[c] = fmax3(mx[c], __uint_as_float(s[c][kx]), __uint_as_float(s[c][kx + 1]));
           const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
           // lazy rescale: move the reference max only when it would grow by > 2^8
           const bool grow = (m_blk > -INFINITY) &&
@@ -901,7 +925,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           if (lane == 0) { MA_EV(33) }
           tc_wait_st();
           tc_fence_before();
-          mbar_arrive(bar_p);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_p);   // 4 arrivals, not 128 serialised ones
           if (lane == 0) { MA_EV(34) }
         }
         // epilogue: O / l -> bf16 -> O_scratch[ft, row, head, :]; tail rows are zeros
@@ -921,7 +946,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           tc_wait_ld();
           if (hh == 1) {            // all of O is in registers: the next task may overwrite it
             tc_fence_before();
-            mbar_arrive(smem_u32(&bars.o_free[wg]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.o_free[wg]));
           }
           stage_row32(stg + hh * kPanel, row, 0, o[0], inv);
           stage_row32(stg + hh * kPanel, row, 32, o[1], inv);
@@ -959,7 +985,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
               tc_wait_ld();
               if (hh == 1) {
                 tc_fence_before();
-                mbar_arrive(smem_u32(&bars.acc_free[h]));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars.acc_free[h]));
               }
               if (valid_m == 128) {
                 // full row tile: stage 64 columns, one TMA store (clipped at `hidden`)
@@ -1002,7 +1029,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             }
           } else {
             tc_fence_before();
-            mbar_arrive(smem_u32(&bars.acc_free[h]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.acc_free[h]));
           }
         }
         // Ordering towards other CTAs / ranks: the leader waits for its TMA stores, rows

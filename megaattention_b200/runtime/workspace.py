@@ -258,6 +258,11 @@ class FusedFaOprojArWorkspace:
         """Attention stage alone (fills ``Oscr``); used by the unfused baseline."""
         self.launch(flags=_cabi.MA_FLAG_FA_ONLY)
 
+    def launch_oproj_only(self):
+        """O_proj stage alone (single rank): ``Oscr`` must hold a finished attention output."""
+        assert self.tp_size == 1
+        self.launch(flags=_cabi.MA_FLAG_OPROJ_ONLY)
+
     def launch_ar_only(self, extra_flags=0):
         """AllReduce stage alone over every slot of ``csym`` (tp > 1).  Every rank's partial
         must be complete before any rank launches (e.g. after a host barrier)."""

@@ -100,3 +100,30 @@ def test_role_weights_do_not_change_results(w):
 def test_few_ctas_and_repeat_launches():
     check(run_case("multi_seq", num_ctas=1))
     check(run_case("chunk_gqa_q4", num_ctas=3, launches=3))
+
+
+def test_stages_run_alone_give_the_fused_result():
+    """Attention-only then O_proj-only launches (the pieces the unfused baseline times)
+    reproduce the fused launch bit for bit."""
+    from megaattention_b200.metadata import build_row_desc
+    from megaattention_b200.runtime import FusedFaOprojArWorkspace
+    name = "chunk_gqa_q4"
+    sq, H, hidden, qpk, sk, seed = CASES[name]
+    Q, K, V, W = make_inputs(name)
+    meta = build_row_desc(sq, seqlens_k=sk)
+    outs = []
+    for staged in (False, True):
+        ws = FusedFaOprojArWorkspace.create(None, meta.num_row_tiles, hidden, H, 128, q_per_kv=qpk,
+                                            max_tot_k=int(meta.cu_seqlens_k[-1]), device="cuda:0")
+        ws.compile(w_fa=2, w_oproj=1, w_ar=0)
+        ws.set_layer(meta, Q.cuda(), K.cuda(), V.cuda(), W.cuda())
+        if staged:
+            ws.launch_fa_only(); ws.check_status()
+            assert ws.ctrl.cpu().tolist() == [0] * 8
+            ws.launch_oproj_only(); ws.check_status()
+        else:
+            ws.launch(); ws.check_status()
+        assert ws.ctrl.cpu().tolist() == [0] * 8
+        outs.append((ws.Oscr.clone(), ws.output(meta)))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1], outs[1][1])
