@@ -1,0 +1,70 @@
+"""Parity at the benchmark configurations' full sizes.
+
+* c2 (13400 tokens, 8 q / 1 kv heads, hidden 4096) and the per-rank shape of c5 (the same
+  queries against a 4x longer KV, q < k) are small enough for the CPU oracle: compared
+  directly, same tolerances as the small cases.
+* c3 (22600 tokens, 64 q / 8 kv heads) is too big for the CPU oracle, so it is checked
+  through a property that does not depend on size: the row-parallel decomposition.  The
+  output of the whole model on one rank must equal the fp32 sum of the eight per-rank
+  partial outputs (each a single-rank launch on that rank's head slice and W_o row slice),
+  up to the bf16 rounding of the nine results.
+"""
+import pytest
+import torch
+
+from megaattention_b200.workloads import WORKLOADS, make_rank_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(wl, tp, rank, dev="cuda:0"):
+    from megaattention_b200.metadata import build_row_desc, choose_launch_config
+    from megaattention_b200.runtime import FusedFaOprojArWorkspace
+    h, hkv = wl.heads_local(tp)
+    Q, K, V, W = make_rank_inputs(wl, tp, rank)
+    meta = build_row_desc(wl.seqlens_q, seqlens_k=wl.seqlens_k)
+    cfg = choose_launch_config(meta, wl.hidden, 1)
+    ws = FusedFaOprojArWorkspace.create(None, meta.num_row_tiles, wl.hidden, h, 128,
+                                        q_per_kv=h // hkv, max_num_batch=meta.num_batch,
+                                        max_tot_k=wl.tot_k, device=dev)
+    ws.compile(w_fa=cfg.w_fa, w_oproj=cfg.w_oproj, w_ar=0)
+    ws.set_layer(meta, Q.to(dev), K.to(dev), V.to(dev), W.to(dev))
+    ws.launch()
+    ws.check_status()
+    assert ws.ctrl.cpu().tolist() == [0] * 8
+    out = ws.output(meta)
+    del ws
+    return (Q, K, V, W), out
+
+
+@pytest.mark.parametrize("name,tol", [("c2", 2e-3), ("c5", 8e-3)])
+def test_full_size_against_cpu_oracle(name, tol):
+    from oracle.chain_oracle import full_chain_oracle, err_beyond_rounding, err_rel
+    wl = WORKLOADS[name]
+    tp = wl.tp_sizes[-1] if name == "c5" else 1
+    torch.set_num_threads(max(1, torch.get_num_threads()))
+    (Q, K, V, W), out = _run(wl, tp, 0)
+    _, Yp, Yf = full_chain_oracle(Q, K, V, W, wl.seqlens_q, wl.seqlens_k)
+    got = out.cpu()
+    e = err_beyond_rounding(got, Yp)
+    print(f"{name}: err_beyond_rounding={e:.3g} err_rel_fp32={err_rel(got, Yp):.3g} "
+          f"err_rel_bf16={err_rel(got, Yf):.3g}")
+    assert e <= tol
+
+
+def test_c3_row_parallel_decomposition():
+    from oracle.chain_oracle import bf16_half_ulp
+    wl = WORKLOADS["c3"]
+    _, full = _run(wl, 1, 0)
+    acc = torch.zeros(full.shape, dtype=torch.float32, device=full.device)
+    slack = torch.zeros_like(acc)
+    for r in range(8):
+        _, part = _run(wl, 8, r)
+        acc += part.float()
+        slack += bf16_half_ulp(part.float())
+    slack += bf16_half_ulp(full.float())
+    ref_max = float(acc.abs().max())
+    excess = ((full.float() - acc).abs() - slack).clamp_min(0.0)
+    e = float(excess.max()) / ref_max
+    print(f"c3 decomposition: excess={e:.3g} raw={(float((full.float() - acc).abs().max()) / ref_max):.3g}")
+    assert e <= 2e-3
