@@ -408,24 +408,30 @@ __device__ __forceinline__ void stage_row32(uint32_t panel, int row, int col0,
 // written back to every rank.  `nthr` threads cooperate; each keeps U 16-byte reductions in
 // flight before its first store (NVLink round trips are microseconds).
 template <int U>
-__device__ __noinline__ void ar_slot(const KParams& p, int ft, int base_out, int vnt, int t,
-                                        int nthr) {
-  const int total = vnt * 2048;                    // 16-byte chunks in the slot
+__device__ __forceinline__ void ar_batch(const KParams& p, int ft, int base_out, int c0, int nthr) {
   auto chunk_addr = [&](int c) -> unsigned long long {
     const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
     const size_t elem =
         ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
     return p.csym_mc + elem * 2;
   };
-  for (int c0 = t; c0 < total; c0 += nthr * U) {
-    uint4 v[U];
+  uint4 v[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u)
-      if (c0 + u * nthr < total) v[u] = multimem_ld_reduce_bf16x8(chunk_addr(c0 + u * nthr));
+  for (int u = 0; u < U; ++u) v[u] = multimem_ld_reduce_bf16x8(chunk_addr(c0 + u * nthr));
 #pragma unroll
-    for (int u = 0; u < U; ++u)
-      if (c0 + u * nthr < total) multimem_st_b128(chunk_addr(c0 + u * nthr), v[u]);
-  }
+  for (int u = 0; u < U; ++u) multimem_st_b128(chunk_addr(c0 + u * nthr), v[u]);
+}
+
+// One AllReduce slot: 128 rows x (vnt x 128) bf16 columns, reduced in the switch and
+// written back to every rank.  `nthr` (256) threads cooperate; each keeps 16 16-byte
+// reductions in flight before its first store (NVLink round trips are microseconds).  A
+// slot is vnt x 2048 chunks: whole batches of nthr x 16, then one of nthr x 8 if vnt is odd.
+__device__ __forceinline__ void ar_slot(const KParams& p, int ft, int base_out, int vnt, int t,
+                                        int nthr) {
+  const int total = vnt * 2048;
+  int c0 = t;
+  for (; c0 + nthr * 15 < total; c0 += nthr * 16) ar_batch<16>(p, ft, base_out, c0, nthr);
+  if (c0 + nthr * 7 < total) ar_batch<8>(p, ft, base_out, c0, nthr);
 }
 
 }  // namespace
@@ -1046,7 +1052,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       } else if (mode == MODE_AR) {
         const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT];
         const int ctid = tid - 128;
-        ar_slot<16>(p, ft, base_out, vnt, ctid, 256);
+        ar_slot(p, ft, base_out, vnt, ctid, 256);
         if (lane == 0) __threadfence_system();   // one per warp; the scheduler fences again
       }
       __syncwarp();
