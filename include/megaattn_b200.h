@@ -82,6 +82,15 @@ typedef struct ma_plan_desc {
   uint64_t peer_ready_count[MA_MAX_TP];         /* per-rank addresses of the symmetric buffers */
   uint64_t peer_ready_bits[MA_MAX_TP];
   uint64_t peer_nvl_signal[MA_MAX_TP];
+  /* Paged KV (src/mega_attention/runtime/workspace.py:67-74, 130-137, 213-222 of the
+   * reference; page size 128 = one key block): when page_table is non-zero, K and V are
+   * caches [max_pages, 128, H_kv, D], key block j of sequence b lives in page
+   * page_table[b * max_pages_per_seq + j], and the KV length of sequence b is
+   * cache_seqlens[b] (cu_k is ignored).  max_tot_k must be max_pages * 128. */
+  uint64_t page_table;      /* i32[max_batch, max_pages_per_seq], or 0: contiguous KV   */
+  uint64_t cache_seqlens;   /* i32[max_batch]                                            */
+  int32_t max_pages_per_seq;
+  int32_t reserved0;
   uint64_t fa_order;   /* i32[max_row_tiles]: row tiles in the order attention tasks are
                           claimed (the workspace sorts longest-first); 0 = natural order.
                           No reference counterpart: the reference claims in tile order. */

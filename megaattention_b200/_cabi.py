@@ -54,6 +54,8 @@ class PlanDesc(C.Structure):
         + [("peer_ready_count", C.c_uint64 * MA_MAX_TP),
            ("peer_ready_bits", C.c_uint64 * MA_MAX_TP),
            ("peer_nvl_signal", C.c_uint64 * MA_MAX_TP),
+           ("page_table", C.c_uint64), ("cache_seqlens", C.c_uint64),
+           ("max_pages_per_seq", C.c_int32), ("reserved0", C.c_int32),
            ("fa_order", C.c_uint64)]
     )
 

@@ -173,6 +173,8 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
                            d->ar_done_bits, d->nvl_signal, d->cu_q, d->cu_k, d->fa_b, d->fa_mb,
                            d->status};
   for (uint64_t a : need) if (a == 0) return MA_ERR_INVALID;
+  if (d->page_table && (!d->cache_seqlens || d->max_pages_per_seq < 1 || d->max_tot_k % 128))
+    return MA_ERR_INVALID;
   if (d->tp_size > 1) {
     if (d->csym_multicast == 0) return MA_ERR_INVALID;
     for (int r = 0; r < d->tp_size; ++r)
@@ -223,6 +225,9 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   k.fa_b = reinterpret_cast<const int*>(d->fa_b);
   k.fa_mb = reinterpret_cast<const int*>(d->fa_mb);
   k.fa_order = reinterpret_cast<const int*>(d->fa_order);
+  k.page_table = reinterpret_cast<const int*>(d->page_table);
+  k.cache_seqlens = reinterpret_cast<const int*>(d->cache_seqlens);
+  k.pps = d->max_pages_per_seq;
   k.status = reinterpret_cast<uint32_t*>(d->status);
   k.csym_mc = d->csym_multicast;
   for (int r = 0; r < MA_MAX_TP; ++r) {

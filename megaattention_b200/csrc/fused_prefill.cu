@@ -617,7 +617,10 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           const int ft = (p.fa_order && !(p.flags & 4u)) ? p.fa_order[pos] : pos;
           const int b = p.fa_b[ft], mb = p.fa_mb[ft];
           const int q0 = p.cu_q[b], q_len = p.cu_q[b + 1] - q0;
-          const int k0 = p.cu_k[b], k_len = p.cu_k[b + 1] - k0;
+          // contiguous KV: rows [k0, k0 + k_len) of K/V; paged KV: k0 is the sequence's row
+          // in the page table and the length comes from cache_seqlens
+          const int k0 = p.page_table ? b * p.pps : p.cu_k[b];
+          const int k_len = p.page_table ? p.cache_seqlens[b] : p.cu_k[b + 1] - k0;
           const int offset = k_len - q_len;
           int nblk = (k_len + 127) >> 7;
           const int nb2 = ((mb + 1) * 128 + offset + 127) >> 7;
@@ -664,8 +667,11 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             tma_load_4d(smem0 + kSmQ + i * kTile, &tmQ, bar, 0, d[TF_QROW0], 0, d[TF_HEAD0] + i);
           }
           const int kvh = d[TF_KVH];
-          int kv_row = d[TF_KSTART] + (nblk - 1) * 128;
-          for (int jj = 0; jj < nblk; ++jj, kv_row -= 128) {
+          const int k_base = d[TF_KSTART];
+          for (int jj = 0; jj < nblk; ++jj) {
+            const int blk = nblk - 1 - jj;
+            // key block -> first row of its 128-row tile (paged: one page is one block)
+            const int kv_row = p.page_table ? p.page_table[k_base + blk] * 128 : k_base + blk * 128;
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
               wait_bar(env, smem_u32(&bars.kv_empty[kv_slot]), kv_ph ^ 1u, 0x10 + kv_slot);

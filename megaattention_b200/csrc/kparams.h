@@ -47,6 +47,9 @@ struct KParams {
   const int* fa_b;
   const int* fa_mb;
   const int* fa_order;            // row tiles in claim order (longest first), or null
+  const int* page_table;          // paged KV: [batch][pps] page of each 128-key block, or null
+  const int* cache_seqlens;       // paged KV: KV length per sequence
+  int pps;                        // page-table row pitch
   uint32_t* status;
 
   unsigned long long csym_mc;

@@ -13,7 +13,7 @@ Differences a caller can observe:
   (``ma_plan_create``) and the role weights / CTA count are launch arguments;
 * ``set_layer`` validates *every* capacity before copying anything;
 * device-side waits are bounded: ``check_status`` raises ``RuntimeError`` when one gave up;
-* ``paged=True`` is not available.
+* role weights and CTA count can change per ``compile`` without any rebuild.
 
 torch is used for device memory, streams and (tp > 1) symmetric-memory bootstrap only.
 """
@@ -60,7 +60,6 @@ class FusedFaOprojArWorkspace:
                max_num_batch=None, max_tot_k=None, dtype=torch.bfloat16, device=None,
                paged=False, page_size=128, max_num_pages=None,
                max_num_pages_per_seq=None):
-        assert not paged, "paged KV is not available in this build"
         assert dtype == torch.bfloat16 and D == 128 and N_TILE == 128
         assert H_local % q_per_kv == 0
         assert 1 <= super_group_n_tiles <= 4, "a super-group is at most 512 TMEM columns"
@@ -76,6 +75,14 @@ class FusedFaOprojArWorkspace:
         tot_cap = max_num_row_tiles * 128
         if max_tot_k is None:
             max_tot_k = tot_cap
+        # paged KV: K/V live in [num_pages, 128, H_kv, D] caches addressed through a page
+        # table; one page is exactly one 128-key block (workspace.py:67-74 of the reference)
+        if paged:
+            assert page_size == N_TILE == 128, (page_size, N_TILE)
+            if max_num_pages is None:
+                max_num_pages = (max_tot_k + 127) // 128
+            if max_num_pages_per_seq is None:
+                max_num_pages_per_seq = (max_tot_k + 127) // 128
         max_owner_slots = (max_total + tp_size - 1) // tp_size
         max_owner_words = (max_owner_slots + 63) // 64
 
@@ -117,7 +124,8 @@ class FusedFaOprojArWorkspace:
             q_per_kv=q_per_kv, num_out=num_out, num_super_groups=nsg,
             max_num_row_tiles=max_num_row_tiles, max_num_batch=max_num_batch,
             max_total_oproj=max_total, tot_cap=tot_cap, max_tot_k=max_tot_k,
-            paged=False, page_size=page_size,
+            paged=bool(paged), page_size=page_size,
+            max_num_pages=max_num_pages, max_num_pages_per_seq=max_num_pages_per_seq,
             ctrl=zeros(NUM_CTRL, torch.uint32), sync_ctrl=zeros(NUM_SYNC, torch.uint32),
             actv=zeros(6, torch.int32), status=zeros(NUM_STATUS, torch.uint32),
             head_ready=zeros(max_num_row_tiles, torch.uint32),
@@ -129,8 +137,13 @@ class FusedFaOprojArWorkspace:
             fa_mb=zeros(max_num_row_tiles, torch.int32),
             fa_order=zeros(max_num_row_tiles, torch.int32),
             Q=zeros((tot_cap, H_local, D), dtype),
-            K=zeros((max_tot_k, H_kv, D), dtype),
-            V=zeros((max_tot_k, H_kv, D), dtype),
+            K=(None if paged else zeros((max_tot_k, H_kv, D), dtype)),
+            V=(None if paged else zeros((max_tot_k, H_kv, D), dtype)),
+            K_cache=(zeros((max_num_pages, 128, H_kv, D), dtype) if paged else None),
+            V_cache=(zeros((max_num_pages, 128, H_kv, D), dtype) if paged else None),
+            page_table=(zeros((max_num_batch, max_num_pages_per_seq), torch.int32)
+                        if paged else None),
+            cache_seqlens=(zeros(max_num_batch, torch.int32) if paged else None),
             W_o=zeros((K_local, hidden_pad), dtype),
             Oscr=zeros((max_num_row_tiles, 128, H_local, D), dtype),
             csym=csym, rco=rco, rbits=rbits, nvl=nvl,
@@ -164,10 +177,16 @@ class FusedFaOprojArWorkspace:
         d.H_local, d.H_kv, d.D, d.hidden = self.H_local, self.H_kv, self.D, self.hidden
         d.super_group_n_tiles = self.super_group_n_tiles
         d.max_row_tiles, d.max_batch = self.max_num_row_tiles, self.max_num_batch
-        d.max_tot_q, d.max_tot_k = self.tot_cap, self.max_tot_k
+        d.max_tot_q = self.tot_cap
+        d.max_tot_k = self.max_num_pages * 128 if self.paged else self.max_tot_k
         d.softmax_scale = float(softmax_scale) if softmax_scale is not None else 0.0
         d.wait_limit_ms = int(wait_limit_ms)
-        for name, t in (("Q", self.Q), ("K", self.K), ("V", self.V), ("W_o", self.W_o),
+        kv = (self.K_cache, self.V_cache) if self.paged else (self.K, self.V)
+        if self.paged:
+            d.page_table = self.page_table.data_ptr()
+            d.cache_seqlens = self.cache_seqlens.data_ptr()
+            d.max_pages_per_seq = self.max_num_pages_per_seq
+        for name, t in (("Q", self.Q), ("K", kv[0]), ("V", kv[1]), ("W_o", self.W_o),
                         ("o_scratch", self.Oscr), ("csym", self.csym), ("ctrl", self.ctrl),
                         ("sync_ctrl", self.sync_ctrl), ("actv", self.actv),
                         ("head_ready", self.head_ready), ("oproj_queue", self.oproj_queue),
@@ -195,24 +214,50 @@ class FusedFaOprojArWorkspace:
         """Copy one layer's inputs and varlen metadata into the active prefixes.
 
         ``Q [tot_q,H_local,D]``, ``K/V [tot_k,H_kv,D]``, ``W_o [K_local,hidden]``; host
-        (pinned) or device tensors.  Raises ``AssertionError`` on any capacity violation
-        before touching the workspace.
+        (pinned) or device tensors.  With ``paged=True`` K/V are the caches
+        ``[num_pages,128,H_kv,D]`` and ``page_table [B,pps]`` / ``cache_seqlens [B]`` (int32)
+        are required.  Raises ``AssertionError`` on any capacity violation before touching
+        the workspace.
         """
-        assert page_table is None and cache_seqlens is None, "paged KV is not available"
         R, nb = meta.num_row_tiles, meta.num_batch
-        tq, tk = Q.shape[0], K.shape[0]
+        tq = Q.shape[0]
         assert R <= self.max_num_row_tiles and nb <= self.max_num_batch
         assert tq <= self.tot_cap
-        assert tk <= self.max_tot_k and V.shape[0] == tk
         assert tuple(Q.shape[1:]) == (self.H_local, self.D)
-        assert tuple(K.shape[1:]) == (self.H_kv, self.D) == tuple(V.shape[1:])
         assert tuple(W_o.shape) == (self.K_local, self.hidden)
-        assert int(meta.cu_seqlens_q[-1]) == tq and int(meta.cu_seqlens_k[-1]) == tk
+        assert int(meta.cu_seqlens_q[-1]) == tq
+        if self.paged:
+            # K, V are caches [num_pages, 128, H_kv, D] (workspace.py:213-222 of the reference)
+            assert page_table is not None and cache_seqlens is not None
+            page_table = torch.as_tensor(page_table, dtype=torch.int32)
+            cache_seqlens = torch.as_tensor(cache_seqlens, dtype=torch.int32)
+            npg, pps = K.shape[0], page_table.shape[1]
+            assert npg <= self.max_num_pages and pps <= self.max_num_pages_per_seq, (
+                npg, self.max_num_pages, pps, self.max_num_pages_per_seq)
+            assert tuple(K.shape[1:]) == (128, self.H_kv, self.D) == tuple(V.shape[1:])
+            assert V.shape[0] == npg and page_table.shape[0] == nb == cache_seqlens.shape[0]
+            lens_k = cache_seqlens.cpu().numpy().astype(np.int64)
+            lens_q = np.diff(np.asarray(meta.cu_seqlens_q, dtype=np.int64))
+            assert bool((lens_k >= lens_q).all()), "q_len > k_len is not supported"
+            assert bool((-(-lens_k // 128) <= pps).all())
+            assert int(page_table.max()) < npg and int(page_table.min()) >= 0
+        else:
+            assert page_table is None and cache_seqlens is None
+            tk = K.shape[0]
+            assert tk <= self.max_tot_k and V.shape[0] == tk
+            assert tuple(K.shape[1:]) == (self.H_kv, self.D) == tuple(V.shape[1:])
+            assert int(meta.cu_seqlens_k[-1]) == tk
         with torch.cuda.stream(self._stream()):
             self.Q[:tq].copy_(Q, non_blocking=True)
             self.W_o[:, :self.hidden].copy_(W_o, non_blocking=True)
-            self.K[:tk].copy_(K, non_blocking=True)
-            self.V[:tk].copy_(V, non_blocking=True)
+            if self.paged:
+                self.K_cache[:npg].copy_(K, non_blocking=True)
+                self.V_cache[:npg].copy_(V, non_blocking=True)
+                self.page_table[:nb, :pps].copy_(page_table.to(self.dev))
+                self.cache_seqlens[:nb].copy_(cache_seqlens.to(self.dev))
+            else:
+                self.K[:tk].copy_(K, non_blocking=True)
+                self.V[:tk].copy_(V, non_blocking=True)
             self._set_meta(meta)
 
     def set_meta(self, meta):
@@ -220,7 +265,7 @@ class FusedFaOprojArWorkspace:
         assert meta.num_row_tiles <= self.max_num_row_tiles
         assert meta.num_batch <= self.max_num_batch
         assert int(meta.cu_seqlens_q[-1]) <= self.tot_cap
-        assert int(meta.cu_seqlens_k[-1]) <= self.max_tot_k
+        assert self.paged or int(meta.cu_seqlens_k[-1]) <= self.max_tot_k
         with torch.cuda.stream(self._stream()):
             self._set_meta(meta)
 

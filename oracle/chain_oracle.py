@@ -66,6 +66,43 @@ def fa_oracle(Q, K, V, seqlens_q, seqlens_k=None, softmax_scale=None):
     return O
 
 
+def make_paged_kv(K, V, seqlens_k, page_size=128, num_pages=None, shuffle=True, seed=0):
+    """Scatter packed ``K/V [tot_k, H_kv, D]`` into a paged cache (follows ``make_paged_kv``,
+    fused.py:121-175, with the same generators so the result is identical on the CPU).
+
+    Returns ``(K_cache, V_cache [num_pages, 128, H_kv, D], page_table [B, max_pps] int32,
+    cache_seqlens [B] int32)``.  Physical pages are a seeded permutation; every slot that
+    holds no valid token (tail of a last page, unused pages) is filled with finite random
+    values, so only masking - not zero fill - keeps them out of the result.
+    """
+    assert page_size == 128
+    lens = [int(x) for x in seqlens_k]
+    B = len(lens)
+    Hkv, D = K.shape[1], K.shape[2]
+    pages_per_seq = [(s + page_size - 1) // page_size for s in lens]
+    total = int(sum(pages_per_seq))
+    if num_pages is None:
+        num_pages = total
+    assert num_pages >= total
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g).tolist() if shuffle else list(range(num_pages))
+    gk = torch.Generator(device="cpu").manual_seed(seed + 11)
+    Kc = torch.randn(num_pages, page_size, Hkv, D, dtype=K.dtype, generator=gk) * 0.2
+    Vc = torch.randn(num_pages, page_size, Hkv, D, dtype=K.dtype, generator=gk) * 0.2
+    table = torch.zeros(B, max(max(pages_per_seq) if B else 0, 1), dtype=torch.int32)
+    nxt, off = 0, 0
+    for b in range(B):
+        for i in range(pages_per_seq[b]):
+            phys = perm[nxt]
+            nxt += 1
+            table[b, i] = phys
+            lo, hi = i * page_size, min((i + 1) * page_size, lens[b])
+            Kc[phys, :hi - lo] = K[off + lo:off + hi]
+            Vc[phys, :hi - lo] = V[off + lo:off + hi]
+        off += lens[b]
+    return Kc, Vc, table, torch.tensor(lens, dtype=torch.int32)
+
+
 def tile_coords(seqlens_q):
     """``(q_tile_start, valid_m)`` per flattened 128-row tile (row_desc.py:96-104)."""
     out = []

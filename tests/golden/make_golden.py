@@ -27,7 +27,7 @@ def main(ref_root):
         build_row_desc, oproj_task_counts, active_counts, csym_numel, oscratch_numel)
     from mega_attention.metadata.launch_heuristic import (
         estimate_work_ratio, choose_launch_config)
-    from mega_attention.reference.fused import full_chain_reference
+    from mega_attention.reference.fused import full_chain_reference, make_paged_kv
 
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     for name, (sq, H, hidden, qpk, sk, seed) in CASES.items():
@@ -43,6 +43,16 @@ def main(ref_root):
             out["o"] = O.numpy()
         np.savez_compressed(os.path.join(HERE, f"chain_{name}.npz"), **out)
         print(name, tuple(Yf.shape), float(Yf.float().abs().max()))
+
+    # paged-KV packer: page table and checksums of the caches for one batch
+    Q, K, V, W = make_inputs("chunk_gqa_q4")
+    sk = CASES["chunk_gqa_q4"][4]
+    Kc, Vc, table, lens = make_paged_kv(K, V, sk, num_pages=sum((s + 127) // 128 for s in sk) + 3,
+                                        shuffle=True, seed=5)
+    np.savez_compressed(os.path.join(HERE, "paged_golden.npz"), page_table=table.numpy(),
+                        cache_seqlens=lens.numpy(),
+                        k_rowsum=Kc.double().sum(dim=(1, 2, 3)).numpy(),
+                        v_rowsum=Vc.double().sum(dim=(1, 2, 3)).numpy())
 
     # host metadata: arrays and scalars for a few batches / shapes
     md = {}

@@ -9,7 +9,7 @@ import torch
 
 from cases import CASES, make_inputs, digest
 from oracle.chain_oracle import (full_chain_oracle, o_scratch_oracle, tile_coords,
-                                 untile_csym, err_rel)
+                                 untile_csym, err_rel, make_paged_kv)
 
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 
@@ -56,3 +56,22 @@ def test_tile_helpers_roundtrip():
     for t, (s, vm) in enumerate(tiles):
         csym.view(5, 128, 256)[t, :vm, :hidden] = Y[s:s + vm]
     assert torch.equal(untile_csym(csym, sq, hidden), Y)
+
+
+def test_paged_packer_matches_reference_fixture():
+    g = np.load(os.path.join(GOLD, "paged_golden.npz"))
+    Q, K, V, W = make_inputs("chunk_gqa_q4")
+    sk = CASES["chunk_gqa_q4"][4]
+    pages = sum((s + 127) // 128 for s in sk) + 3
+    Kc, Vc, table, lens = make_paged_kv(K, V, sk, num_pages=pages, shuffle=True, seed=5)
+    assert (table.numpy() == g["page_table"]).all() and table.dtype == torch.int32
+    assert (lens.numpy() == g["cache_seqlens"]).all()
+    assert np.array_equal(Kc.double().sum(dim=(1, 2, 3)).numpy(), g["k_rowsum"])
+    assert np.array_equal(Vc.double().sum(dim=(1, 2, 3)).numpy(), g["v_rowsum"])
+    # gathering the pages back gives the packed tensors
+    off = 0
+    for b, lk in enumerate(sk):
+        for i in range((lk + 127) // 128):
+            n = min(128, lk - i * 128)
+            assert torch.equal(Kc[int(table[b, i]), :n], K[off + i * 128: off + i * 128 + n])
+        off += lk
