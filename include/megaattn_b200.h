@@ -125,6 +125,17 @@ int ma_plan_create(const ma_plan_desc* desc, ma_plan** out);
  * layer: the kernel ends with a cross-rank barrier. */
 int ma_launch(ma_plan* plan, const ma_launch_args* args, void* stream);
 
+/* Point the plan at caller-owned inputs instead of the workspace's capacity buffers: the
+ * TMA descriptors of Q, K, V and W_o are re-encoded over the given tensors, nothing is
+ * copied.  The reference copies Q/K/V/W_o into the workspace on every layer
+ * (workspace.py:210-231); this is the in-place alternative.  Q [tot_q, H_local, D],
+ * K/V [tot_k, H_kv, D] (or the caches [tot_k/128, 128, H_kv, D] of a paged plan), W_o
+ * [K_local, w_width] with hidden <= w_width and w_width % 64 == 0 (columns past the width
+ * are read as zeros).  All 16-byte aligned, bf16, contiguous; they must stay valid until the
+ * launch that uses them has finished.  Host-side only; takes effect at the next ma_launch. */
+int ma_plan_set_inputs(ma_plan* plan, uint64_t Q, uint64_t K, uint64_t V, uint64_t W_o,
+                       int64_t tot_q, int64_t tot_k, int64_t w_width);
+
 /* Reads the device status block (synchronises `stream` first).  No reference
  * counterpart: the reference's device waits are unbounded. */
 int ma_read_status(ma_plan* plan, void* stream, ma_status* out);

@@ -25,7 +25,7 @@ MA_ERR_NOT_SM100 = -3
 MA_ERR_DEVICE_TIMEOUT = -4
 MA_ERR_CAPACITY = -5
 
-EXPORTS = ("ma_query_device", "ma_plan_create", "ma_launch", "ma_read_status",
+EXPORTS = ("ma_query_device", "ma_plan_create", "ma_launch", "ma_plan_set_inputs", "ma_read_status",
            "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc")
 
 MA_NOALLOC_OSCRATCH_BYTES = 16 << 20
@@ -97,6 +97,8 @@ def _load():
     lib.ma_plan_create.restype = C.c_int
     lib.ma_launch.argtypes = [C.c_void_p, C.POINTER(LaunchArgs), C.c_void_p]
     lib.ma_launch.restype = C.c_int
+    lib.ma_plan_set_inputs.argtypes = [C.c_void_p] + [C.c_uint64] * 4 + [C.c_int64] * 3
+    lib.ma_plan_set_inputs.restype = C.c_int
     lib.ma_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(Status)]
     lib.ma_read_status.restype = C.c_int
     lib.ma_plan_destroy.argtypes = [C.c_void_p]

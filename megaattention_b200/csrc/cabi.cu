@@ -25,6 +25,7 @@ struct ma_plan {
   CUtensorMap maps[6];   // Q, K, V, O_scratch (2-D), W_o, C_sym (store)
   int device;
   int num_sms;
+  ma_plan_desc desc;     // as given at creation (shapes for re-encoding)
 };
 
 namespace {
@@ -193,6 +194,7 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   memset(pl, 0, sizeof(*pl));
   pl->device = d->device;
   pl->num_sms = sms;
+  pl->desc = *d;
 
   ma::KParams& k = pl->kp;
   k.H = d->H_local; k.Hkv = d->H_kv; k.q_per_kv = d->H_local / d->H_kv;
@@ -260,6 +262,26 @@ int ma_launch(ma_plan* pl, const ma_launch_args* a, void* stream) {
   if (n > pl->num_sms) n = pl->num_sms;          // grid barrier needs every CTA resident
   cudaError_t e = ma::launch_fused_prefill(pl->maps, kp, n, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? MA_OK : MA_ERR_CUDA;
+}
+
+int ma_plan_set_inputs(ma_plan* pl, uint64_t Q, uint64_t K, uint64_t V, uint64_t W_o,
+                       int64_t tot_q, int64_t tot_k, int64_t w_width) {
+  if (!pl || !Q || !K || !V || !W_o) return MA_ERR_INVALID;
+  const ma_plan_desc& d = pl->desc;
+  if (tot_q < 1 || tot_k < 1 || w_width < d.hidden || w_width % 64) return MA_ERR_INVALID;
+  if (d.page_table && tot_k % 128) return MA_ERR_INVALID;
+  CUtensorMap fresh[6];
+  const int rc = ma::encode_path_maps(fresh, Q, K, V, d.o_scratch, W_o,
+                                      static_cast<uint64_t>(d.H_local),
+                                      static_cast<uint64_t>(d.H_kv),
+                                      static_cast<uint64_t>(tot_q), static_cast<uint64_t>(tot_k),
+                                      static_cast<uint64_t>(d.max_row_tiles),
+                                      static_cast<uint64_t>(w_width), d.csym,
+                                      static_cast<uint64_t>(d.hidden),
+                                      static_cast<uint64_t>(pl->kp.num_out) * 128);
+  if (rc != MA_OK) return rc;
+  pl->maps[0] = fresh[0]; pl->maps[1] = fresh[1]; pl->maps[2] = fresh[2]; pl->maps[4] = fresh[4];
+  return MA_OK;
 }
 
 int ma_read_status(ma_plan* pl, void* stream, ma_status* out) {

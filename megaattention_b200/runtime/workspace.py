@@ -247,6 +247,7 @@ class FusedFaOprojArWorkspace:
             assert tk <= self.max_tot_k and V.shape[0] == tk
             assert tuple(K.shape[1:]) == (self.H_kv, self.D) == tuple(V.shape[1:])
             assert int(meta.cu_seqlens_k[-1]) == tk
+        self._unbind()
         with torch.cuda.stream(self._stream()):
             self.Q[:tq].copy_(Q, non_blocking=True)
             self.W_o[:, :self.hidden].copy_(W_o, non_blocking=True)
@@ -259,6 +260,52 @@ class FusedFaOprojArWorkspace:
                 self.K[:tk].copy_(K, non_blocking=True)
                 self.V[:tk].copy_(V, non_blocking=True)
             self._set_meta(meta)
+
+    def bind_inputs(self, meta, Q, K, V, W_o, page_table=None, cache_seqlens=None):
+        """Zero-copy alternative to ``set_layer``: the kernel reads the caller's device
+        tensors in place (only the varlen metadata is uploaded).  ``W_o`` may be the plain
+        ``[K_local, hidden]`` weight when ``hidden % 64 == 0``, else a zero-padded
+        ``[K_local, hidden_pad]`` one.  The tensors must stay alive and unchanged until the
+        launch has finished; a later ``set_layer`` goes back to the workspace's own buffers.
+        """
+        for t in (Q, K, V, W_o):
+            assert t.is_cuda and t.device == self.dev and t.dtype == self.dtype
+            assert t.is_contiguous() and t.data_ptr() % 16 == 0
+        R, nb = meta.num_row_tiles, meta.num_batch
+        assert R <= self.max_num_row_tiles and nb <= self.max_num_batch
+        assert tuple(Q.shape[1:]) == (self.H_local, self.D) and Q.shape[0] <= self.tot_cap
+        assert int(meta.cu_seqlens_q[-1]) == Q.shape[0]
+        assert W_o.shape[0] == self.K_local and W_o.shape[1] >= self.hidden and W_o.shape[1] % 64 == 0
+        if self.paged:
+            assert page_table is not None and cache_seqlens is not None
+            assert tuple(K.shape[1:]) == (128, self.H_kv, self.D) == tuple(V.shape[1:])
+            tot_k = K.shape[0] * 128
+            page_table = torch.as_tensor(page_table, dtype=torch.int32)
+            cache_seqlens = torch.as_tensor(cache_seqlens, dtype=torch.int32)
+            assert page_table.shape[1] <= self.max_num_pages_per_seq
+            assert int(page_table.max()) < K.shape[0] and int(page_table.min()) >= 0
+        else:
+            assert tuple(K.shape[1:]) == (self.H_kv, self.D) == tuple(V.shape[1:])
+            tot_k = K.shape[0]
+            assert int(meta.cu_seqlens_k[-1]) == tot_k
+        _cabi.check(_cabi.lib.ma_plan_set_inputs(
+            self._plan, Q.data_ptr(), K.data_ptr(), V.data_ptr(), W_o.data_ptr(),
+            int(Q.shape[0]), int(tot_k), int(W_o.shape[1])), "ma_plan_set_inputs")
+        self._bound = (Q, K, V, W_o)          # keep them alive
+        with torch.cuda.stream(self._stream()):
+            if self.paged:
+                self.page_table[:nb, :page_table.shape[1]].copy_(page_table.to(self.dev))
+                self.cache_seqlens[:nb].copy_(cache_seqlens.to(self.dev))
+            self._set_meta(meta)
+
+    def _unbind(self):
+        if getattr(self, "_bound", None) is not None:
+            kv = (self.K_cache, self.V_cache) if self.paged else (self.K, self.V)
+            tot_k = self.max_num_pages * 128 if self.paged else self.max_tot_k
+            _cabi.check(_cabi.lib.ma_plan_set_inputs(
+                self._plan, self.Q.data_ptr(), kv[0].data_ptr(), kv[1].data_ptr(),
+                self.W_o.data_ptr(), self.tot_cap, tot_k, self.hidden_pad), "ma_plan_set_inputs")
+            self._bound = None
 
     def set_meta(self, meta):
         """Metadata only (inputs already resident in ``self.Q/K/V/W_o``)."""

@@ -127,3 +127,30 @@ def test_stages_run_alone_give_the_fused_result():
         outs.append((ws.Oscr.clone(), ws.output(meta)))
     assert torch.equal(outs[0][0], outs[1][0])
     assert torch.equal(outs[0][1], outs[1][1])
+
+
+def test_bound_inputs_give_the_same_result_as_copied_inputs():
+    """Zero-copy path (ma_plan_set_inputs): the kernel reads the caller's tensors in place,
+    with an unpadded W_o, and gives the same bits as the copying set_layer path; going
+    back to set_layer afterwards works too."""
+    from megaattention_b200.metadata import build_row_desc
+    from megaattention_b200.runtime import FusedFaOprojArWorkspace
+    name = "chunk_multiseq"                 # hidden 384: unpadded W_o is [256, 384]
+    sq, H, hidden, qpk, sk, seed = CASES[name]
+    Q, K, V, W = make_inputs(name)
+    meta = build_row_desc(sq, seqlens_k=sk)
+    ws = FusedFaOprojArWorkspace.create(None, meta.num_row_tiles + 3, hidden, H, 128, q_per_kv=qpk,
+                                        max_tot_k=int(meta.cu_seqlens_k[-1]) + 100, device="cuda:0")
+    ws.compile(w_fa=2, w_oproj=1, w_ar=0)
+    ws.set_layer(meta, Q.cuda(), K.cuda(), V.cuda(), W.cuda())
+    ws.launch(); ws.check_status()
+    ref = ws.output(meta).clone()
+    ws.csym.zero_(); ws.Q.zero_(); ws.K.zero_(); ws.V.zero_(); ws.W_o.zero_()
+    Qd, Kd, Vd, Wd = Q.cuda(), K.cuda(), V.cuda(), W.cuda().contiguous()
+    ws.bind_inputs(meta, Qd, Kd, Vd, Wd)
+    ws.launch(); ws.check_status()
+    assert torch.equal(ws.output(meta), ref)
+    ws.csym.zero_()
+    ws.set_layer(meta, Qd, Kd, Vd, Wd)
+    ws.launch(); ws.check_status()
+    assert torch.equal(ws.output(meta), ref)
