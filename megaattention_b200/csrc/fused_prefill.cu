@@ -308,35 +308,14 @@ __device__ __noinline__ void publish_ar_ready(const KParams& p, int slot) {
   atom_add_release_gpu(p.ctrl + C_OP_DONE, 1u);
 }
 
-// ---------------------------------------------------------------- grid / rank barriers
-// Grid barrier on one sync word: CTA 0 adds 0x80000000-(G-1), the others add 1, so one
-// episode flips only the top bit and the word never needs zeroing
-// (fused_fa_oproj_ar.py:74-96).  The spin is bounded.
-__device__ __noinline__ void grid_sync(const Env& e, int idx) {
-  __syncthreads();
-  if (threadIdx.x == 0 && !*e.abort_flag) {
-    const KParams& p = *e.p;
-    const uint32_t delta = (blockIdx.x == 0) ? (0x80000000u - (gridDim.x - 1)) : 1u;
-    const uint32_t old = atom_add_release_gpu(p.sync_ctrl + idx, delta);
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t it = 0;
-    while (((ld_acquire_gpu(p.sync_ctrl + idx) ^ old) & 0x80000000u) == 0) {
-      if ((++it & 63u) == 0) {
-        if (ld_relaxed_gpu(p.status) != 0u) { *e.abort_flag = 1; break; }
-        if (globaltimer_ns() - t0 > p.wait_limit_ns) { report(e, ST_TIMEOUT_GRID, idx, old); break; }
-      }
-    }
-  }
-  __syncthreads();
-}
-
+// ---------------------------------------------------------------- rank barrier
 // Cross-rank barrier at kernel exit: two signal slots (phase) counted up to tp and back
 // down to 0 (sign), selected by a rank-local counter, so it is reusable without any reset
-// (fused_fa_oproj_ar.py:99-143).  CTA 0 only.
+// (fused_fa_oproj_ar.py:99-143).  Run by one CTA (the last one to finish).
 __device__ __noinline__ void rank_barrier(const Env& e) {
   const KParams& p = *e.p;
   __syncthreads();
-  if (blockIdx.x == 0 && !*e.abort_flag) {
+  if (!*e.abort_flag) {
     const uint32_t st = ld_relaxed_gpu(p.sync_ctrl + S_NVL_COUNTER);
     const int phase = st & 1u;
     const int down = (st >> 1) & 1u;
@@ -1082,20 +1061,27 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
 #undef MA_TASK_DONE
 
   // ------------------------------------------------------------------ exit protocol
-  // quiesce -> every CTA clears the per-launch control state at full capacity -> all
-  // cleared -> (tp > 1) one cross-rank barrier, which also opens the next launch
+  // The reference ends with grid barrier -> every CTA clears the per-launch control state
+  // -> grid barrier -> cross-rank barrier (fused_fa_oproj_ar.py:1154-1177).  Here each CTA
+  // only counts itself out; the last one to do so (every other CTA has stopped touching
+  // the control words by then) clears the state at full capacity, resets the counter and,
+  // with tp > 1, runs the cross-rank barrier that also opens the next launch.  No CTA
+  // waits for another one.
   __syncthreads();
   if (!s_abort) {
-    grid_sync(env, S_GS_QUIESCE);
-    if (!s_abort) {
-      const int stride = gridDim.x * kThreads;
-      const int g0 = blockIdx.x * kThreads + tid;
-      for (int i = g0; i < p.max_row_tiles; i += stride) p.head_ready[i] = 0u;
-      for (int i = g0; i < p.max_owner_slots; i += stride) p.ready_count[i] = 0u;
-      for (int i = g0; i < p.max_owner_words; i += stride) { p.ready_bits[i] = 0ull; p.ar_done_bits[i] = 0ull; }
-      if (blockIdx.x == 0 && tid < 8) p.ctrl[tid] = 0u;
-      __threadfence();
-      grid_sync(env, S_GS_CLEANDONE);
+    __shared__ int s_last;
+    if (tid == 0) {
+      fence_acq_rel_gpu();
+      s_last = (atom_add_acqrel_gpu(p.sync_ctrl + S_GS_QUIESCE, 1u) == gridDim.x - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      for (int i = tid; i < p.max_row_tiles; i += kThreads) p.head_ready[i] = 0u;
+      for (int i = tid; i < p.max_owner_slots; i += kThreads) p.ready_count[i] = 0u;
+      for (int i = tid; i < p.max_owner_words; i += kThreads) { p.ready_bits[i] = 0ull; p.ar_done_bits[i] = 0ull; }
+      if (tid < 8) p.ctrl[tid] = 0u;
+      if (tid == 8) p.sync_ctrl[S_GS_QUIESCE] = 0u;
+      __threadfence_system();
       if (p.tp > 1 && !(p.flags & (1u | 16u))) rank_barrier(env);
     }
   }
