@@ -59,6 +59,7 @@ struct Bars {
   uint64_t op_empty[4];
   uint64_t acc_full[2];     // MMA: O_proj accumulator half h complete
   uint64_t acc_free[2];     // epilogue warps: half h read out (count 8)
+  uint64_t drain[2];        // abort path only: an issuer's outstanding MMAs have retired
   uint64_t dbg;             // trace builds only
 };
 
@@ -468,6 +469,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       mbar_init(smem_u32(&bars.op_full[i]), 1);
       mbar_init(smem_u32(&bars.op_empty[i]), 1);
     }
+    mbar_init(smem_u32(&bars.drain[0]), 1);
+    mbar_init(smem_u32(&bars.drain[1]), 1);
     mbar_init(smem_u32(&bars.dbg), 1);
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -509,7 +512,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
   prev_mode = mode_var; prev_k = slot_k; slot_k ^= 1;
 
   if (warp < 4) {
-    reg_dec<64>();
+    reg_dec<80>();
     if (warp == 2 && lane == 0) {
       // ==================================================================== scheduler
       const int num_fa = p.actv[0];
@@ -803,7 +806,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     __syncwarp();
   } else {
     // ====================================================================== compute warps
-    reg_inc<216>();
+    reg_inc<208>();
     const int wg = (warp - 4) >> 2;                            // compute warpgroup 0 / 1
     const int row = (warp & 3) * 32 + lane;                    // TMEM lane == tile row
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -1086,6 +1089,22 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     }
   }
 
+  if (s_abort) {
+    // A wait ran out (here or in another CTA) and the roles left their loops wherever they
+    // were: MMAs, TMA loads and TMA stores of this CTA may still be in flight, and none of
+    // them may outlive the CTA's shared memory and TMEM.  Each issuer waits (bounded) for
+    // its own MMAs, the store leaders for their bulk stores, and everybody gives loads
+    // already issued 100 us to land (nothing issues new ones any more).
+    if ((warp == 1 || warp == 3) && lane == 0) {
+      const uint32_t bar = smem_u32(&bars.drain[warp == 1 ? 0 : 1]);
+      tc_commit(bar);
+      for (int it = 0; it < (1 << 20); ++it)
+        if (mbar_try_wait(bar, 0)) break;
+    }
+    if ((warp == 4 || warp == 8) && lane == 0) tma_store_wait_all();
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 100000ull) {}
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
