@@ -176,6 +176,8 @@ def main():
     ap.add_argument("--stage", default="fused", choices=["fused", "fa", "ar", "oproj"],
                     help="fa / ar: time the attention / AllReduce stage alone (profiling aid)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-p2p", action="store_true",
+                    help="tp 2: reduce through multimem instead of peer loads (comparison)")
     ap.add_argument("--per-rank-heads", type=int, default=0,
                     help="experiment: every rank gets this many q heads (1 kv head), c3 sequences")
     ap.add_argument("--flags", type=int, default=None,
@@ -226,6 +228,7 @@ def main():
     ws.compile(w_fa=w[0], w_oproj=w[1], w_ar=w[2], num_ctas=args.ctas or None)
     ws.set_layer(meta, Qh, Kh, Vh, Wh)
     torch.cuda.synchronize()
+    ws.ar_p2p = not args.no_p2p
     ws.default_flags = (args.flags if args.flags is not None
                         else launch_flags_b200(meta, wl.hidden, tp, h))
 

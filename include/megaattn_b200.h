@@ -44,6 +44,10 @@ typedef enum ma_error {
                                  all ranks' partials must already be in place             */
 #define MA_FLAG_NO_AR 16u     /* stop after O_proj: C_sym holds this rank's partial (measurement aid) */
 #define MA_FLAG_OPROJ_ONLY 32u /* O_proj stage only (single rank): O_scratch must be complete */
+#define MA_FLAG_AR_P2P 64u     /* tp_size == 2 only: the slot owner reduces with plain peer loads and
+                                  stores through peer_csym instead of multimem (with two GPUs the
+                                  multicast path runs far below the NVLink copy rate).  Same sum:
+                                  fp32, rounded once.  No reference counterpart. */
 #define MA_FLAG_TILE_ORDER 4u /* claim attention tasks in row-tile order, ignoring fa_order */
 
 typedef struct ma_devinfo {
@@ -94,6 +98,9 @@ typedef struct ma_plan_desc {
   uint64_t fa_order;   /* i32[max_row_tiles]: row tiles in the order attention tasks are
                           claimed (the workspace sorts longest-first); 0 = natural order.
                           No reference counterpart: the reference claims in tile order. */
+  uint64_t peer_csym[MA_MAX_TP];   /* per-rank addresses of C_sym (symmetric); needed for
+                                      MA_FLAG_AR_P2P, may be 0 otherwise.  No reference
+                                      counterpart: the reference reduces through multimem only. */
 } ma_plan_desc;
 
 /* Role weights etc.: the arguments of FusedFaOprojArWorkspace.compile()

@@ -17,6 +17,7 @@ MA_FLAG_TILE_ORDER = 4
 MA_FLAG_AR_ONLY = 8
 MA_FLAG_NO_AR = 16
 MA_FLAG_OPROJ_ONLY = 32
+MA_FLAG_AR_P2P = 64
 
 MA_OK = 0
 MA_ERR_INVALID = -1
@@ -56,7 +57,8 @@ class PlanDesc(C.Structure):
            ("peer_nvl_signal", C.c_uint64 * MA_MAX_TP),
            ("page_table", C.c_uint64), ("cache_seqlens", C.c_uint64),
            ("max_pages_per_seq", C.c_int32), ("reserved0", C.c_int32),
-           ("fa_order", C.c_uint64)]
+           ("fa_order", C.c_uint64),
+           ("peer_csym", C.c_uint64 * MA_MAX_TP)]
     )
 
 

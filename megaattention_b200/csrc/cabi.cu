@@ -236,6 +236,7 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
     k.peer_rc[r] = d->peer_ready_count[r];
     k.peer_rb[r] = d->peer_ready_bits[r];
     k.peer_nvl[r] = d->peer_nvl_signal[r];
+    k.peer_csym[r] = d->peer_csym[r];
   }
 
   const uint64_t H = d->H_local, Hkv = d->H_kv;
@@ -256,6 +257,9 @@ int ma_launch(ma_plan* pl, const ma_launch_args* a, void* stream) {
   kp.w_fa = a->w_fa; kp.w_oproj = a->w_oproj;
   kp.w_ar = (kp.tp > 1) ? a->w_ar : 0;          // one rank: no AllReduce role
   kp.flags = a->flags;
+  if ((kp.flags & MA_FLAG_AR_P2P) &&
+      (kp.tp != 2 || !pl->desc.peer_csym[0] || !pl->desc.peer_csym[1]))
+    return MA_ERR_INVALID;
   if (kp.w_fa < 0 || kp.w_oproj < 0 || kp.w_ar < 0 || kp.w_fa + kp.w_oproj + kp.w_ar < 1)
     return MA_ERR_INVALID;
   int n = a->num_ctas > 0 ? a->num_ctas : pl->num_sms;

@@ -402,6 +402,34 @@ __device__ __forceinline__ void ar_batch(const KParams& p, int ft, int base_out,
   for (int u = 0; u < U; ++u) multimem_st_b128(chunk_addr(c0 + u * nthr), v[u]);
 }
 
+// The same batch with plain peer loads and stores, two ranks only: the owner reads its own
+// and the peer's partial, adds in fp32, rounds once and writes both copies.  With two GPUs
+// the multicast path is several times slower than the NVLink copy rate; this one is not.
+template <int U>
+__device__ __forceinline__ void ar_batch_p2p(const KParams& p, int ft, int base_out, int c0, int nthr) {
+  auto chunk_off = [&](int c) -> unsigned long long {
+    const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
+    const size_t elem =
+        ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
+    return elem * 2;
+  };
+  const unsigned long long mine = p.peer_csym[p.rank], peer = p.peer_csym[p.rank ^ 1];
+  uint4 a[U], b[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) b[u] = ld_relaxed_sys_b128(peer + chunk_off(c0 + u * nthr));
+#pragma unroll
+  for (int u = 0; u < U; ++u) a[u] = ld_relaxed_sys_b128(mine + chunk_off(c0 + u * nthr));
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    uint4 r;
+    r.x = add_bf16x2_via_f32(a[u].x, b[u].x); r.y = add_bf16x2_via_f32(a[u].y, b[u].y);
+    r.z = add_bf16x2_via_f32(a[u].z, b[u].z); r.w = add_bf16x2_via_f32(a[u].w, b[u].w);
+    const unsigned long long off = chunk_off(c0 + u * nthr);
+    st_relaxed_sys_b128(peer + off, r);
+    st_relaxed_sys_b128(mine + off, r);
+  }
+}
+
 // One AllReduce slot: 128 rows x (vnt x 128) bf16 columns, reduced in the switch and
 // written back to every rank.  `nthr` (256) threads cooperate; each keeps 16 16-byte
 // reductions in flight before its first store (NVLink round trips are microseconds).  A
@@ -410,6 +438,10 @@ __device__ __forceinline__ void ar_slot(const KParams& p, int ft, int base_out, 
                                         int nthr) {
   const int total = vnt * 2048;
   int c0 = t;
+  if (p.flags & 64u) {      // MA_FLAG_AR_P2P (host side admits it at tp == 2 only)
+    for (; c0 + nthr * 7 < total; c0 += nthr * 8) ar_batch_p2p<8>(p, ft, base_out, c0, nthr);
+    return;
+  }
   for (; c0 + nthr * 15 < total; c0 += nthr * 16) ar_batch<16>(p, ft, base_out, c0, nthr);
   if (c0 + nthr * 7 < total) ar_batch<8>(p, ft, base_out, c0, nthr);
 }
@@ -862,60 +894,116 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
               for (int kx = 0; kx < 32; ++kx)
                 if (c * 32 + kx > lim) s[c][kx] = 0xff800000u;   // -inf
           }
-          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          // Fast path (every block after the first that needs no mask): the exponentials do
+          // not wait for this block's row maximum.  They are taken against the reference
+          // maximum as it stands while the block maximum is computed alongside; only if
+          // some row of the warp turns out to need a new reference (growth beyond 2^8,
+          // rare after the first block) the scores are read again from TMEM, where P has
+          // not been stored over them yet, and the block goes down the ordinary path.
+          // Scale-and-subtract and the row sums work on packed pairs (fma / add on two
+          // floats per instruction): the loop is short of issue slots, not of pipes.
+          bool done = false;
+          if (jj > 0 && !need_mask) {
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * sl2;
+            const uint64_t sl2x2 = pack_f32x2(sl2, sl2), negm2 = pack_f32x2(neg_m, neg_m);
+            uint64_t sum2[2] = {pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f)};
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int kx = 0; kx < 32; kx += 2)
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-              mx[c] = fmax3(mx[c], __uint_as_float(s[c][kx]), __uint_as_float(s[c][kx + 1]));
-          const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-          // lazy rescale: move the reference max only when it would grow by > 2^8
-          const bool grow = (m_blk > -INFINITY) &&
-                            ((m_ref == -INFINITY) || ((m_blk - m_ref) * sl2 > kRescaleThreshold));
-          float o_scale = 1.f;
-          if (grow) {
-            o_scale = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_blk) * sl2);
-            m_ref = m_blk;
-            l_run *= o_scale;
-          }
-          if (jj > 0 && __any_sync(0xffffffffu, grow)) {
-            // the P V MMA of the previous block completed before this block's S was
-            // committed (in-order tensor pipe), so O is quiescent here
-#pragma unroll 1
             for (int c = 0; c < 4; ++c) {
-              uint32_t o[32];
-              tmem_ld32(t_o + c * 32, o);
-              tc_wait_ld();
+              uint32_t pk[16];
 #pragma unroll
-              for (int kx = 0; kx < 32; ++kx)
-                o[kx] = __float_as_uint(__uint_as_float(o[kx]) * o_scale);
-              tmem_st32(t_o + c * 32, o);
+              for (int kx = 0; kx < 16; ++kx) {
+                const float x0 = __uint_as_float(s[c][2 * kx]), x1 = __uint_as_float(s[c][2 * kx + 1]);
+                mx[kx & 3] = fmax3(mx[kx & 3], x0, x1);
+                const uint64_t a2 = fma_f32x2(pack_f32x2(x0, x1), sl2x2, negm2);
+                float a0, a1;
+                unpack_f32x2(a2, a0, a1);
+                const float e0 = ex2(a0), e1 = ex2(a1);
+                sum2[kx & 1] = add_f32x2(sum2[kx & 1], pack_f32x2(e0, e1));
+                pk[kx] = pack_bf16x2(e0, e1);
+              }
+              if ((c & 1) == 0) {
+#pragma unroll
+                for (int kx = 0; kx < 16; ++kx) s[c][kx] = pk[kx];
+              } else {
+#pragma unroll
+                for (int kx = 0; kx < 16; ++kx) s[c - 1][16 + kx] = pk[kx];
+              }
             }
-          }
-          if (lane == 0) { MA_EV(32) }
-          const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * sl2;
-          float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int kx = 0; kx < 16; ++kx) {
-              const float e0 = ex2(fmaf(__uint_as_float(s[c][2 * kx]), sl2, neg_m));
-              const float e1 = ex2(fmaf(__uint_as_float(s[c][2 * kx + 1]), sl2, neg_m));
-              sum[(kx & 1) * 2] += e0; sum[(kx & 1) * 2 + 1] += e1;
-              pk[kx] = pack_bf16x2(e0, e1);
-            }
-            // 16 packed columns per 32 scores: two chunks fill one 32-column store
-            if ((c & 1) == 0) {
-#pragma unroll
-              for (int kx = 0; kx < 16; ++kx) s[c][kx] = pk[kx];
+            float s0, s1, s2, s3;
+            unpack_f32x2(sum2[0], s0, s1);
+            unpack_f32x2(sum2[1], s2, s3);
+            const float l_blk = (s0 + s1) + (s2 + s3);
+            const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            const bool grow = (m_blk > -INFINITY) &&
+                              ((m_ref == -INFINITY) || ((m_blk - m_ref) * sl2 > kRescaleThreshold));
+            if (!__any_sync(0xffffffffu, grow)) {
+              tmem_st32(t_s, s[0]);
+              tmem_st32(t_s + 32, s[2]);
+              l_run += l_blk;
+              done = true;
             } else {
 #pragma unroll
-              for (int kx = 0; kx < 16; ++kx) s[c - 1][16 + kx] = pk[kx];
-              tmem_st32(t_s + (c >> 1) * 32, s[c - 1]);
+              for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
+              tc_wait_ld();
             }
           }
-          l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+          if (!done) {
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int kx = 0; kx < 32; kx += 2)
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                mx[c] = fmax3(mx[c], __uint_as_float(s[c][kx]), __uint_as_float(s[c][kx + 1]));
+            const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            // lazy rescale: move the reference max only when it would grow by > 2^8
+            const bool grow = (m_blk > -INFINITY) &&
+                              ((m_ref == -INFINITY) || ((m_blk - m_ref) * sl2 > kRescaleThreshold));
+            float o_scale = 1.f;
+            if (grow) {
+              o_scale = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_blk) * sl2);
+              m_ref = m_blk;
+              l_run *= o_scale;
+            }
+            if (jj > 0 && __any_sync(0xffffffffu, grow)) {
+              // the P V MMA of the previous block completed before this block's S was
+              // committed (in-order tensor pipe), so O is quiescent here
+#pragma unroll 1
+              for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(t_o + c * 32, o);
+                tc_wait_ld();
+#pragma unroll
+                for (int kx = 0; kx < 32; ++kx)
+                  o[kx] = __float_as_uint(__uint_as_float(o[kx]) * o_scale);
+                tmem_st32(t_o + c * 32, o);
+              }
+            }
+            if (lane == 0) { MA_EV(32) }
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * sl2;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int kx = 0; kx < 16; ++kx) {
+                const float e0 = ex2(fmaf(__uint_as_float(s[c][2 * kx]), sl2, neg_m));
+                const float e1 = ex2(fmaf(__uint_as_float(s[c][2 * kx + 1]), sl2, neg_m));
+                sum[(kx & 1) * 2] += e0; sum[(kx & 1) * 2 + 1] += e1;
+                pk[kx] = pack_bf16x2(e0, e1);
+              }
+              // 16 packed columns per 32 scores: two chunks fill one 32-column store
+              if ((c & 1) == 0) {
+#pragma unroll
+                for (int kx = 0; kx < 16; ++kx) s[c][kx] = pk[kx];
+              } else {
+#pragma unroll
+                for (int kx = 0; kx < 16; ++kx) s[c - 1][16 + kx] = pk[kx];
+                tmem_st32(t_s + (c >> 1) * 32, s[c - 1]);
+              }
+            }
+            l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+          }
           if (lane == 0) { MA_EV(33) }
           tc_wait_st();
           tc_fence_before();

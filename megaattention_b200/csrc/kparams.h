@@ -56,6 +56,7 @@ struct KParams {
   unsigned long long peer_rc[kMaxTp];
   unsigned long long peer_rb[kMaxTp];
   unsigned long long peer_nvl[kMaxTp];
+  unsigned long long peer_csym[kMaxTp];   // every rank's C_sym (peer-load AllReduce, tp 2)
 };
 
 constexpr int kThreads = 384;

@@ -242,6 +242,25 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed pairs of fp32 (sm_100 has fma / add on two floats per instruction).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -351,6 +370,26 @@ __device__ __forceinline__ uint64_t atom_or_release_sys_u64(uint64_t* p, uint64_
 }
 
 // ------------------------------------------------------------------ NVLS multimem
+// 16-byte load / store at system scope (another GPU's memory over NVLink, or this one's).
+__device__ __forceinline__ uint4 ld_relaxed_sys_b128(uint64_t addr) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_b128(uint64_t addr, uint4 v) {
+  asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1,%2,%3,%4};"
+               ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// bf16x2 + bf16x2 with the sum taken in fp32 and rounded once (what the switch does).
+__device__ __forceinline__ uint32_t add_bf16x2_via_f32(uint32_t a, uint32_t b) {
+  const float lo = __uint_as_float(a << 16) + __uint_as_float(b << 16);
+  const float hi = __uint_as_float(a & 0xFFFF0000u) + __uint_as_float(b & 0xFFFF0000u);
+  return pack_bf16x2(lo, hi);
+}
 // Sum of the 8 bf16 at the same offset on every rank of the multicast object, fp32
 // accumulation in the switch; the result comes back as 4 packed bf16x2 words.
 __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(uint64_t mc_addr) {

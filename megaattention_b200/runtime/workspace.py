@@ -52,6 +52,7 @@ class FusedFaOprojArWorkspace:
         self._args = None
         self._meta = None
         self.default_flags = 0   # OR of _cabi.MA_FLAG_* applied by launch()
+        self.ar_p2p = True       # tp_size == 2: AllReduce through peer loads instead of multimem
 
     # ------------------------------------------------------------------ create
     @classmethod
@@ -108,6 +109,7 @@ class FusedFaOprojArWorkspace:
             rc_ptrs = [int(hRC.buffer_ptrs[r]) for r in range(tp_size)]
             rb_ptrs = [int(hRB.buffer_ptrs[r]) for r in range(tp_size)]
             nvl_peer_ptrs = [int(hN.buffer_ptrs[r]) for r in range(tp_size)]
+            csym_peer_ptrs = [int(hC.buffer_ptrs[r]) for r in range(tp_size)]
             handles = (hC, hRC, hRB, hN)
         else:
             csym = zeros((max_num_row_tiles, 128, num_out, N_TILE), dtype)
@@ -115,7 +117,7 @@ class FusedFaOprojArWorkspace:
             rbits = zeros(max_owner_words, torch.int64)
             nvl = zeros(2, torch.int32)
             csym_mc_ptr = 0
-            rc_ptrs, rb_ptrs, nvl_peer_ptrs = [], [], []
+            rc_ptrs, rb_ptrs, nvl_peer_ptrs, csym_peer_ptrs = [], [], [], []
 
         ws = cls(
             dev=dev, dtype=dtype, tp_size=tp_size, rank=rank, group_name=group_name,
@@ -147,7 +149,7 @@ class FusedFaOprojArWorkspace:
             W_o=zeros((K_local, hidden_pad), dtype),
             Oscr=zeros((max_num_row_tiles, 128, H_local, D), dtype),
             csym=csym, rco=rco, rbits=rbits, nvl=nvl,
-            csym_mc_ptr=csym_mc_ptr, nvl_peer_ptrs=nvl_peer_ptrs,
+            csym_mc_ptr=csym_mc_ptr, nvl_peer_ptrs=nvl_peer_ptrs, csym_peer_ptrs=csym_peer_ptrs,
             rc_ptrs=rc_ptrs, rb_ptrs=rb_ptrs, _handles=handles,
         )
         # The first launch relies on every control word being zero on every rank before
@@ -201,6 +203,7 @@ class FusedFaOprojArWorkspace:
             d.peer_ready_count[r] = self.rc_ptrs[r]
             d.peer_ready_bits[r] = self.rb_ptrs[r]
             d.peer_nvl_signal[r] = self.nvl_peer_ptrs[r]
+            d.peer_csym[r] = self.csym_peer_ptrs[r]
         plan = C.c_void_p()
         _cabi.check(_cabi.lib.ma_plan_create(C.byref(d), C.byref(plan)), "ma_plan_create")
         self._plan = plan
@@ -341,6 +344,9 @@ class FusedFaOprojArWorkspace:
     def launch(self, flags=None):
         assert self._plan is not None, "call compile() first"
         flags = self.default_flags if flags is None else flags
+        if self.tp_size == 2 and self.ar_p2p:
+            # two GPUs: reduce with peer loads/stores, not multimem (see MA_FLAG_AR_P2P)
+            flags |= _cabi.MA_FLAG_AR_P2P
         args = _cabi.LaunchArgs(self._args.w_fa, self._args.w_oproj, self._args.w_ar,
                                 self._args.num_ctas, int(flags))
         _cabi.check(_cabi.lib.ma_launch(self._plan, C.byref(args),
