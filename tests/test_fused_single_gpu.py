@@ -154,3 +154,23 @@ def test_bound_inputs_give_the_same_result_as_copied_inputs():
     ws.set_layer(meta, Qd, Kd, Vd, Wd)
     ws.launch(); ws.check_status()
     assert torch.equal(ws.output(meta), ref)
+
+
+def test_peer_load_allreduce_flag_is_refused_on_one_rank():
+    """MA_FLAG_AR_P2P needs two ranks and their C_sym addresses: on one rank the launch is
+    rejected on the host, nothing runs and the workspace stays usable."""
+    from megaattention_b200 import _cabi
+    from megaattention_b200.metadata import build_row_desc
+    from megaattention_b200.runtime import FusedFaOprojArWorkspace
+    name = "multi_seq"
+    sq, H, hidden, qpk, sk, seed = CASES[name]
+    Q, K, V, W = make_inputs(name)
+    meta = build_row_desc(sq, seqlens_k=sk)
+    ws = FusedFaOprojArWorkspace.create(None, meta.num_row_tiles, hidden, H, 128, q_per_kv=qpk,
+                                        max_tot_k=int(meta.cu_seqlens_k[-1]), device="cuda:0")
+    ws.compile(w_fa=2, w_oproj=1, w_ar=0)
+    ws.set_layer(meta, Q.cuda(), K.cuda(), V.cuda(), W.cuda())
+    with pytest.raises(RuntimeError):
+        ws.launch(flags=_cabi.MA_FLAG_AR_P2P)
+    ws.launch(); ws.check_status()
+    assert ws.ctrl.cpu().tolist() == [0] * 8
