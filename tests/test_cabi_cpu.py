@@ -68,3 +68,36 @@ def test_shape_validation_happens_before_any_device_call():
     assert _cabi.lib.ma_fused_prefill_noalloc(C.byref(a), None) == _cabi.MA_ERR_INVALID
     a.hidden, a.num_batch = 128, 513
     assert _cabi.lib.ma_fused_prefill_noalloc(C.byref(a), None) == _cabi.MA_ERR_CAPACITY
+
+
+def test_ctypes_mirror_agrees_with_the_compiled_header(tmp_path):
+    """Compile the header with the C compiler and compare sizeof / offsetof of every field
+    of every struct with the ctypes mirror (the hand-computed numbers above only pin a few)."""
+    import shutil
+    import subprocess
+    cc = shutil.which("gcc") or shutil.which("cc")
+    assert cc, "a C compiler is part of the build environment"
+    pairs = {"ma_devinfo": _cabi.DevInfo, "ma_plan_desc": _cabi.PlanDesc,
+             "ma_launch_args": _cabi.LaunchArgs, "ma_status": _cabi.Status,
+             "ma_noalloc_args": _cabi.NoAllocArgs}
+    lines = ['#include <stdio.h>', '#include <stddef.h>',
+             '#include "%s"' % os.path.join(ROOT, "include", "megaattn_b200.h"),
+             'int main(void) {']
+    for cname, ct in pairs.items():
+        lines.append('  printf("%s sizeof %%zu\\n", sizeof(%s));' % (cname, cname))
+        for fname, *_ in ct._fields_:
+            lines.append('  printf("%s %s %%zu\\n", offsetof(%s, %s));' % (cname, fname, cname, fname))
+    lines += ['  return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([cc, "-std=c99", "-o", str(exe), str(src)], check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    seen = 0
+    for ln in out.splitlines():
+        cname, fname, val = ln.split()
+        ct = pairs[cname]
+        want = C.sizeof(ct) if fname == "sizeof" else getattr(ct, fname).offset
+        assert int(val) == want, (cname, fname, val, want)
+        seen += 1
+    assert seen == sum(len(ct._fields_) + 1 for ct in pairs.values())
