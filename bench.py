@@ -8,10 +8,12 @@
 
 A step is one fused launch over one batch of synthetic input (one layer of prefill).
 N = 1 runs workload c2 (one GPU, tp = 1); N > 1 runs the tensor-parallel sweep c3 with
-tp = N (fixed global model: strong scaling).  The printed line follows the build's bench
-contract; the method mirrors the reference's benchmarks/bench_fused_fa_oproj_ar.py:75-131,
-158-312 (L2 flushed before every timed launch, device time, max over ranks, the same FLOP
-and byte formulas, an unfused FA + cuBLAS + NVLS-AllReduce baseline beside it).
+tp = N (fixed global model: strong scaling; the N = 1 line carries c3 at tp 1 as
+``scaling_anchor``).  The method mirrors the reference's
+benchmarks/bench_fused_fa_oproj_ar.py:75-131, 158-312: L2 flushed before every timed
+launch, device time, max over ranks, the same FLOP and byte formulas, an unfused
+FA + cuBLAS + AllReduce baseline beside it, and the fused output cross-checked against
+that baseline's (``parity``).
 """
 from __future__ import annotations
 
@@ -36,6 +38,9 @@ from megaattention_b200.metadata.launch_heuristic import launch_flags_b200  # no
 
 METRIC = "fused_fa_oproj_ar_prefill_tflops"
 UNIT = "TFLOP/s"
+NVLINK_GBS_NOMINAL = 900.0      # per direction per GPU
+NVLINK_GBS_PEER_COPY = 770.0    # peer copy rate measured on this pool
+TENSOR_TFLOPS_NOMINAL = 2250.0  # dense bf16
 
 
 def _peaks():
@@ -95,16 +100,20 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def workload_name(wl, tp):
+    return f"{wl.name} tp{tp}"
+
+
 def cpu_chain_sample(wl, tp, rank, max_seconds_hint=25.0):
     """Time the CPU oracle on a bounded sample of the workload: whole sequences of rank
-    `rank`, longest first, until the estimated cost passes the hint.  Returns
-    (tflops, seconds, threads, description)."""
+    `rank`, shortest first, until the estimated cost passes the hint.  Returns
+    (tflops, seconds, threads, description, chosen sequence indices, Y_partial fp32)."""
     from oracle.chain_oracle import full_chain_oracle
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     Q, K, V, W = make_rank_inputs(wl, tp, rank)
     h, hkv = wl.heads_local(tp)
-    # pick a prefix of sequences (in batch order) worth roughly the hint at ~0.15 TFLOP/s
+    # pick sequences worth roughly the hint at ~0.15 TFLOP/s
     budget = max_seconds_hint * 0.15e12
     cq = [0]; ck = [0]
     for a, b in zip(wl.seqlens_q, wl.seqlens_k):
@@ -123,12 +132,12 @@ def cpu_chain_sample(wl, tp, rank, max_seconds_hint=25.0):
     Ks = torch.cat([K[ck[i]:ck[i + 1]] for i in chosen])
     Vs = torch.cat([V[ck[i]:ck[i + 1]] for i in chosen])
     t0 = time.perf_counter()
-    full_chain_oracle(Qs, Ks, Vs, W, sq, sk)
+    _, Yp, _ = full_chain_oracle(Qs, Ks, Vs, W, sq, sk)
     dt = time.perf_counter() - t0
     desc = (f"{wl.name} rank {rank}/{tp}: sequences {sq} of {wl.seqlens_q} "
             f"({cost / 1e9:.1f} of {(fa_flops(wl.seqlens_q, h, 128, wl.seqlens_k) + oproj_flops(wl.tot_q, h * 128, wl.hidden)) / 1e9:.1f} GFLOP), "
             f"fp32 torch CPU oracle, {threads} threads")
-    return cost / dt / 1e12, dt, threads, desc
+    return cost / dt / 1e12, dt, threads, desc, chosen, Yp
 
 
 def run_reference(args, wl, tp):
@@ -137,27 +146,84 @@ def run_reference(args, wl, tp):
         return
     vals, descs = [], None
     for i in range(args.warmup + args.steps):
-        v, dt, threads, desc = cpu_chain_sample(wl, tp, 0, max_seconds_hint=args.cpu_seconds)
+        v, dt, threads, desc, _, _ = cpu_chain_sample(wl, tp, 0, max_seconds_hint=args.cpu_seconds)
         if i >= args.warmup:
             vals.append((v, dt))
         descs = (threads, desc)
     v = sum(x for x, _ in vals) / len(vals)
     ms = 1e3 * sum(d for _, d in vals) / len(vals)
-    h, _ = wl.heads_local(tp)
+    h, hkv = wl.heads_local(tp)
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{wl.name} tp{tp} (bounded CPU sample per step)",
-                   "seqlens_q": wl.seqlens_q, "kv_mult": wl.kv_mult, "H_local": h,
-                   "hidden": wl.hidden},
+        "config": {"workload": workload_name(wl, tp), "seqlens_q": wl.seqlens_q,
+                   "kv_mult": wl.kv_mult, "H_local": h, "H_kv": hkv, "hidden": wl.hidden},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": descs[0], "kind": "port",
                          "sample": descs[1]},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------- error figures (device)
+def _half_ulp_bf16(x):
+    a = x.float().abs().clamp_min(2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(a)) - 8.0)
+
+
+def _err_figures(got_bf16, ref_fp32, slack_extra=None):
+    """``err_rel`` = max|got - bf16(ref)| / max|ref| (the reference bench's figure,
+    benchmarks/bench_fused_fa_oproj_ar.py:259-270) and the same maximum taken beyond the
+    rounding any bf16 result carries (half a bf16 ulp of the fp32 value, plus the ranks'
+    partials' half-ulps when given)."""
+    g = got_bf16.float()
+    ref_max = float(ref_fp32.abs().max().clamp_min(1e-30))
+    raw = float((g - ref_fp32.to(torch.bfloat16).float()).abs().max()) / ref_max
+    slack = _half_ulp_bf16(ref_fp32)
+    if slack_extra is not None:
+        slack = slack + slack_extra
+    beyond = float(((g - ref_fp32).abs() - slack).clamp_min(0).max()) / ref_max
+    return raw, beyond, ref_max
+
+
+def library_attention(dev):
+    """The attention leg of the unfused baseline from a library, as in the reference's
+    bench (flash_attn_varlen_func, bench_fused_fa_oproj_ar.py:43,247): flash-attn if its
+    kernels run on this GPU, else torch's scaled_dot_product_attention per sequence."""
+    try:
+        from flash_attn import flash_attn_varlen_func
+        q = torch.randn(256, 2, 128, device=dev, dtype=torch.bfloat16)
+        cu = torch.tensor([0, 256], device=dev, dtype=torch.int32)
+        flash_attn_varlen_func(q, q[:, :1].contiguous(), q[:, :1].contiguous(), cu, cu, 256, 256,
+                               causal=True)
+        torch.cuda.synchronize(dev)
+
+        def run(Q, K, V, cu_q, cu_k, sq, sk):
+            return flash_attn_varlen_func(Q, K, V, cu_q, cu_k, max(sq), max(sk), causal=True)
+        return "flash_attn %s flash_attn_varlen_func" % __import__("flash_attn").__version__, run
+    except Exception:
+        import torch.nn.functional as F
+
+        def run(Q, K, V, cu_q, cu_k, sq, sk):
+            out = torch.empty_like(Q)
+            q0 = k0 = 0
+            for lq, lk in zip(sq, sk):
+                q = Q[q0:q0 + lq].transpose(0, 1)[None]
+                k = K[k0:k0 + lk].transpose(0, 1)[None]
+                v = V[k0:k0 + lk].transpose(0, 1)[None]
+                if lq == lk:
+                    o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+                else:        # causal mask aligned bottom-right
+                    keep = (torch.arange(lk, device=Q.device)[None, :]
+                            <= torch.arange(lq, device=Q.device)[:, None] + (lk - lq))
+                    o = F.scaled_dot_product_attention(q, k, v, attn_mask=keep, enable_gqa=True)
+                out[q0:q0 + lq] = o[0].transpose(0, 1)
+                q0 += lq; k0 += lk
+            return out
+        return "torch %s scaled_dot_product_attention per sequence" % torch.__version__, run
 
 
 def main():
@@ -171,17 +237,15 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-unfused", action="store_true")
-    ap.add_argument("--w", type=str, default=None, help="w_fa,w_oproj,w_ar override")
-    ap.add_argument("--ctas", type=int, default=0)
-    ap.add_argument("--stage", default="fused", choices=["fused", "fa", "ar", "oproj"],
-                    help="fa / ar: time the attention / AllReduce stage alone (profiling aid)")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-p2p", action="store_true",
-                    help="tp 2: reduce through multimem instead of peer loads (comparison)")
-    ap.add_argument("--per-rank-heads", type=int, default=0,
-                    help="experiment: every rank gets this many q heads (1 kv head), c3 sequences")
-    ap.add_argument("--flags", type=int, default=None,
-                    help="launch flags (2: drain downstream work first, 4: row-tile claim order)")
+    ap.add_argument("--no-anchor", action="store_true")
+    # launch configuration (defaults: the reference heuristic's role weights, this library's
+    # launch flags); the sweep summarised under profiles/ was made with these
+    ap.add_argument("--w", type=str, default=None, help="w_fa,w_oproj,w_ar")
+    ap.add_argument("--ctas", type=int, default=0)
+    ap.add_argument("--flags", type=int, default=None, help="launch flags (MA_FLAG_* bits)")
+    ap.add_argument("--stage", default="fused", choices=["fused", "fa", "ar", "oproj", "noar"],
+                    help="time one stage of the kernel alone (what the profiles/ captures ran)")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -189,10 +253,6 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     tp = args.tp or max(world, 1)
     wl = WORKLOADS[args.workload or ("c2" if tp == 1 else "c3")]
-    if args.per_rank_heads:
-        from megaattention_b200.workloads import Workload
-        wl = Workload(f"{wl.name}-h{args.per_rank_heads}", wl.seqlens_q, args.per_rank_heads * tp, tp,
-                      wl.hidden, [tp], kv_mult=wl.kv_mult, per_rank_seed=True)
     if args.impl == "reference":
         if args.steps > 3:
             args.steps = 3
@@ -200,6 +260,8 @@ def main():
         return run_reference(args, wl, tp)
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    assert not (args.stage == "ar" and tp == 1), "--stage ar needs more than one GPU"
+    assert not (args.stage == "oproj" and tp > 1), "--stage oproj is single-GPU"
     W = max(args.warmup, 3)
     K = args.steps
     dev = torch.device(f"cuda:{local_rank}")
@@ -212,6 +274,7 @@ def main():
         group = dist.group.WORLD.group_name
         symm_mem.enable_symm_mem_for_group(group)
 
+    from megaattention_b200 import _cabi
     from megaattention_b200.runtime import FusedFaOprojArWorkspace
     h, hkv = wl.heads_local(tp)
     Q, Kt, V, Wo = make_rank_inputs(wl, tp, rank)
@@ -221,16 +284,20 @@ def main():
     w = (cfg.w_fa, cfg.w_oproj, cfg.w_ar)
     if args.w:
         w = tuple(int(x) for x in args.w.split(","))
-    ws = FusedFaOprojArWorkspace.create(
-        group, max_num_row_tiles=meta.num_row_tiles, hidden=wl.hidden, H_local=h, D=128,
-        tp_size=tp, rank=rank, super_group_n_tiles=cfg.sg, q_per_kv=h // hkv,
-        max_num_batch=meta.num_batch, max_tot_k=wl.tot_k, device=dev)
-    ws.compile(w_fa=w[0], w_oproj=w[1], w_ar=w[2], num_ctas=args.ctas or None)
+    flags = args.flags if args.flags is not None else launch_flags_b200(meta, wl.hidden, tp, h)
+
+    def make_ws():
+        x = FusedFaOprojArWorkspace.create(
+            group, max_num_row_tiles=meta.num_row_tiles, hidden=wl.hidden, H_local=h, D=128,
+            tp_size=tp, rank=rank, super_group_n_tiles=cfg.sg, q_per_kv=h // hkv,
+            max_num_batch=meta.num_batch, max_tot_k=wl.tot_k, device=dev)
+        x.compile(w_fa=w[0], w_oproj=w[1], w_ar=w[2], num_ctas=args.ctas or None)
+        x.default_flags = flags
+        return x
+
+    ws = make_ws()
     ws.set_layer(meta, Qh, Kh, Vh, Wh)
     torch.cuda.synchronize()
-    ws.ar_p2p = not args.no_p2p
-    ws.default_flags = (args.flags if args.flags is not None
-                        else launch_flags_b200(meta, wl.hidden, tp, h))
 
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)   # 4 x L2
     stream = torch.cuda.current_stream()
@@ -263,7 +330,8 @@ def main():
     if sampler:
         sampler.start()
     stage_fn = {"fused": ws.launch, "fa": ws.launch_fa_only,
-                "ar": lambda: ws.launch_ar_only((args.flags or 0) & ~0xF),
+                "ar": lambda: ws.launch_ar_only(flags & ~0xFF),
+                "noar": lambda: ws.launch(flags=(flags | _cabi.MA_FLAG_NO_AR)),
                 "oproj": ws.launch_oproj_only}[args.stage]
     ms_fused = timed(stage_fn, K, W)
     clocks = sampler.stop() if sampler else None
@@ -275,44 +343,73 @@ def main():
     S = ar_bytes(wl.tot_q, wl.hidden)
     bus = S * 2 * (tp - 1) / tp
     peaks = _peaks()
-    t_comp = flops_rank / (peaks["tflops"] * 1e12)
-    t_ar = bus / 770e9
-    roofline = {
-        "bound": "tensor" if t_comp >= t_ar else "nvlink",
-        "achieved": flops_rank / (ms_fused * 1e-3) / 1e12, "peak": peaks["tflops"],
-        "unit": "TFLOP/s", "frac": (flops_rank / (ms_fused * 1e-3) / 1e12) / peaks["tflops"],
+    # Roofline: the slower of the compute leg (FLOPs at the bf16 tensor peak) and the
+    # AllReduce leg (bus bytes at 900 GB/s per direction).  Which leg is slower is decided
+    # at nominal peaks, as the target is stated; the figure reported against the measured
+    # tensor peak is kept next to it.
+    t_comp_nom = flops_rank / (TENSOR_TFLOPS_NOMINAL * 1e12)
+    t_comp_meas = flops_rank / (peaks["tflops"] * 1e12)
+    t_ar_nom = bus / (NVLINK_GBS_NOMINAL * 1e9)
+    tensor_achieved = flops_rank / (ms_fused * 1e-3) / 1e12
+    if t_ar_nom > t_comp_nom:
+        roofline = {"bound": "nvlink", "achieved": bus / (ms_fused * 1e-3) / 1e9,
+                    "peak": NVLINK_GBS_NOMINAL, "unit": "GB/s",
+                    "frac": t_ar_nom * 1e3 / ms_fused, "peak_source": "nominal per direction"}
+    else:
+        roofline = {"bound": "tensor", "achieved": tensor_achieved, "peak": peaks["tflops"],
+                    "unit": "TFLOP/s", "frac": tensor_achieved / peaks["tflops"],
+                    "peak_source": peaks["source"]}
+    roofline.update({
         # dram read+write bytes of one launch from an ncu capture (profiles/): c2, tp 1 only
         "traffic": 147.5e6 if (wl.name == "c2" and tp == 1 and args.stage == "fused") else None,
-        "traffic_unit": "bytes/launch", "peak_source": peaks["source"],
-        "t_compute_ms": t_comp * 1e3, "t_allreduce_ms": t_ar * 1e3,
-        "frac_of_slower_leg": max(t_comp, t_ar) * 1e3 / ms_fused,
-        "nominal": {"t_compute_ms_2250tf": flops_rank / 2250e12 * 1e3,
-                    "t_allreduce_ms_900gbs": bus / 900e9 * 1e3,
-                    "frac": max(flops_rank / 2250e12, bus / 900e9) * 1e3 / ms_fused},
-    }
+        "traffic_unit": "bytes/launch",
+        "tensor_tflops": tensor_achieved, "tensor_frac_of_measured": tensor_achieved / peaks["tflops"],
+        "tensor_frac_of_nominal": tensor_achieved / TENSOR_TFLOPS_NOMINAL,
+        "t_compute_ms_nominal": t_comp_nom * 1e3, "t_compute_ms_measured_peak": t_comp_meas * 1e3,
+        "t_allreduce_ms_900gbs": t_ar_nom * 1e3,
+        "frac_of_slower_leg_nominal": max(t_comp_nom, t_ar_nom) * 1e3 / ms_fused,
+        "frac_of_slower_leg_measured": max(t_comp_meas, bus / (NVLINK_GBS_PEER_COPY * 1e9)) * 1e3 / ms_fused,
+    })
+
+    # ---- strong-scaling anchor: the tensor-parallel workload on one GPU ---------------
+    anchor = None
+    if tp == 1 and args.workload is None and args.stage == "fused" and not args.no_anchor:
+        wa = WORKLOADS["c3"]
+        ha, hkva = wa.heads_local(1)
+        Qa, Ka, Va, Wa = make_rank_inputs(wa, 1, 0)
+        ma = build_row_desc(wa.seqlens_q, seqlens_k=wa.seqlens_k)
+        ca = choose_launch_config(ma, wa.hidden, 1)
+        wsa = FusedFaOprojArWorkspace.create(
+            None, ma.num_row_tiles, wa.hidden, ha, 128, super_group_n_tiles=ca.sg,
+            q_per_kv=ha // hkva, max_num_batch=ma.num_batch, max_tot_k=wa.tot_k, device=dev)
+        wsa.compile(w_fa=ca.w_fa, w_oproj=ca.w_oproj, w_ar=0)
+        wsa.set_layer(ma, Qa, Ka, Va, Wa)
+        ms_a = timed(wsa.launch, max(3, min(K, 10)), 3)
+        wsa.check_status()
+        fl_a = fa_flops(wa.seqlens_q, ha, 128, wa.seqlens_k) + oproj_flops(wa.tot_q, ha * 128, wa.hidden)
+        anchor = {"workload": workload_name(wa, 1), "ms": ms_a, "tflops": fl_a / (ms_a * 1e-3) / 1e12,
+                  "frac_of_measured_peak": fl_a / (ms_a * 1e-3) / 1e12 / peaks["tflops"]}
+        del wsa, Qa, Ka, Va, Wa
 
     # ---- end-to-end through the public API with host buffers ------------------------
-    # Every step copies its inputs from pinned host memory, launches, and reads the whole
-    # result back.  On one GPU two workspaces on two streams take turns, so one step's
-    # copies overlap the other's (PCIe is full duplex); with tp > 1 the steps stay on one
-    # stream: two launches per rank could reach the GPUs in different orders on different
-    # ranks and wait on each other.
+    # Every step copies its inputs from pinned host memory, launches, and reads the result
+    # back: the whole output on one GPU, this rank's 1/tp share of the rows (the output is
+    # replicated) with tp > 1.  Two workspaces on two streams take turns, so one step's
+    # copies overlap the other's (PCIe is full duplex); each launch waits for the previous
+    # one, so the ranks run their launches in the same order.
     lanes = [(ws, torch.cuda.current_stream(dev))]
-    if world == 1 and not args.no_e2e:
+    if not args.no_e2e:
         side = torch.cuda.Stream(dev)
         with torch.cuda.stream(side):
-            ws2 = FusedFaOprojArWorkspace.create(
-                group, max_num_row_tiles=meta.num_row_tiles, hidden=wl.hidden, H_local=h, D=128,
-                tp_size=tp, rank=rank, super_group_n_tiles=cfg.sg, q_per_kv=h // hkv,
-                max_num_batch=meta.num_batch, max_tot_k=wl.tot_k, device=dev)
-            ws2.compile(w_fa=w[0], w_oproj=w[1], w_ar=w[2], num_ctas=args.ctas or None)
-            ws2.default_flags = ws.default_flags
+            ws2 = make_ws()
         side.synchronize()
         lanes.append((ws2, side))
-    host_outs = [torch.empty(ws.csym[:meta.num_row_tiles].shape, dtype=torch.bfloat16).pin_memory()
+    R = meta.num_row_tiles
+    r_lo, r_hi = (rank * R) // tp, ((rank + 1) * R) // tp
+    host_outs = [torch.empty(ws.csym[r_lo:r_hi].shape, dtype=torch.bfloat16).pin_memory()
                  for _ in lanes]
-    host_out = host_outs[0]
     e2e_i = [0]
+    last_kernel = [None]
 
     def e2e_step():
         i = e2e_i[0] % len(lanes)
@@ -320,10 +417,15 @@ def main():
         w_i, s_i = lanes[i]
         with torch.cuda.stream(s_i):
             w_i.set_layer(meta, Qh, Kh, Vh, Wh)
+            if last_kernel[0] is not None:
+                s_i.wait_event(last_kernel[0])
             w_i.launch()
-            host_outs[i].copy_(w_i.csym[:meta.num_row_tiles], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(s_i)
+            last_kernel[0] = ev
+            host_outs[i].copy_(w_i.csym[r_lo:r_hi], non_blocking=True)
 
-    n_e2e = 0 if args.no_e2e else max(3, min(K, 10))
+    n_e2e = 0 if args.no_e2e else max(4, min(K, 10))
     for _ in range(2 if n_e2e else 0):
         e2e_step()
     torch.cuda.synchronize(); barrier()
@@ -336,59 +438,107 @@ def main():
         t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = float(t.item())
-    h2d = sum(t.numel() * 2 for t in (Q, Kt, V, Wo)) + 4 * (2 * (meta.num_batch + 1) + 2 * meta.num_row_tiles + 6)
-    d2h = host_out.numel() * 2
+    h2d = sum(t.numel() * 2 for t in (Q, Kt, V, Wo)) + 4 * (2 * (meta.num_batch + 1) + 3 * R + 6)
+    d2h = host_outs[0].numel() * 2
     e2e = {"value": flops_job / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-           "streams": len(lanes)}
+           "streams": len(lanes), "bytes": "per rank"}
     for w_i, _ in lanes:
         w_i.check_status()
+    lanes = lanes[:1]
 
-    # ---- unfused baseline on the same box: FA kernel, cuBLAS GEMM, NVLS AllReduce ----
+    # ---- unfused baseline on the same box: attention, cuBLAS GEMM, AllReduce ---------
     unfused = None
-    if not args.no_unfused:
-        ms_fa = timed(ws.launch_fa_only, max(3, K // 2), 3)
+    parity = None
+    cu_q = torch.tensor(meta.cu_seqlens_q, dtype=torch.int32, device=dev)
+    cu_k = torch.tensor(meta.cu_seqlens_k, dtype=torch.int32, device=dev)
+    if not args.no_unfused and args.stage == "fused":
+        nrep = max(3, K // 2)
+        ms_fa_own = timed(ws.launch_fa_only, nrep, 3)
         ws.check_status()
-        A = ws.Oscr.view(-1, ws.K_local)[:wl.tot_q]
+        lib_name, lib_fa = library_attention(dev)
+        Qd, Kd, Vd = ws.Q[:wl.tot_q], ws.K[:wl.tot_k], ws.V[:wl.tot_k]
+        ms_fa_lib = timed(lambda: lib_fa(Qd, Kd, Vd, cu_q, cu_k, wl.seqlens_q, wl.seqlens_k), nrep, 3)
+        A = torch.empty(wl.tot_q, ws.K_local, dtype=torch.bfloat16, device=dev).normal_()
         Wd = Wo.to(dev)
         Y = torch.empty(wl.tot_q, wl.hidden, dtype=torch.bfloat16, device=dev)
-        ms_gemm = timed(lambda: torch.matmul(A, Wd, out=Y), max(3, K // 2), 3)
-        ms_ar = 0.0
+        ms_gemm = timed(lambda: torch.matmul(A, Wd, out=Y), nrep, 3)
+        ms_ar = ms_ar_nvls = ms_ar_nccl = 0.0
         if world > 1:
             import torch.distributed._symmetric_memory as symm_mem
             Ys = symm_mem.empty(wl.tot_q, wl.hidden, dtype=torch.bfloat16, device=dev)
             symm_mem.rendezvous(Ys, group)
             Ys.zero_()
             ms_ar_nvls = timed(lambda: torch.ops.symm_mem.multimem_all_reduce_(Ys, "sum", group),
-                               max(3, K // 2), 3)
-            ms_ar_nccl = timed(lambda: dist.all_reduce(Y), max(3, K // 2), 3)
+                               nrep, 3)
+            ms_ar_nccl = timed(lambda: dist.all_reduce(Y), nrep, 3)
             ms_ar = min(ms_ar_nvls, ms_ar_nccl)
+        ms_fa = min(ms_fa_own, ms_fa_lib)
         serial = ms_fa + ms_gemm + ms_ar
-        unfused = {"fa_ms": ms_fa, "oproj_cublas_ms": ms_gemm, "allreduce_ms": ms_ar,
-                   "allreduce_symm_mem_multimem_ms": ms_ar_nvls if world > 1 else 0.0,
-                   "allreduce_nccl_ms": ms_ar_nccl if world > 1 else 0.0,
-                   "serial_ms": serial, "ideal_ms": max(ms_fa + ms_gemm, ms_ar),
+        unfused = {"fa_ms": ms_fa, "fa_library_ms": ms_fa_lib, "fa_library": lib_name,
+                   "fa_own_stage_ms": ms_fa_own, "oproj_cublas_ms": ms_gemm, "allreduce_ms": ms_ar,
+                   "allreduce_symm_mem_multimem_ms": ms_ar_nvls, "allreduce_nccl_ms": ms_ar_nccl,
+                   "serial_ms": serial, "serial_with_library_fa_ms": ms_fa_lib + ms_gemm + ms_ar,
+                   "ideal_ms": max(ms_fa + ms_gemm, ms_ar),
                    "ratio_serial_over_fused": serial / ms_fused,
-                   "fa": "this library's attention stage alone (MA_FLAG_FA_ONLY)"}
+                   "ratio_serial_library_fa_over_fused": (ms_fa_lib + ms_gemm + ms_ar) / ms_fused,
+                   "note": "serial_ms takes the faster attention leg (library kernel or this "
+                           "library's attention stage alone) and the faster AllReduce"}
+
+        # ---- parity: the fused output against the unfused chain on the same inputs ----
+        # attention from the library kernel (an implementation that shares nothing with the
+        # fused kernel), O_proj as an fp32 matmul, AllReduce as an fp32 sum over the ranks;
+        # compared over the valid region of every tile.
+        ws.launch(); ws.check_status()
+        fused = ws.output(meta)
+        O_lib = lib_fa(Qd, Kd, Vd, cu_q, cu_k, wl.seqlens_q, wl.seqlens_k)
+        ref = O_lib.reshape(wl.tot_q, -1).float() @ Wd.float()
+        slack = None
+        if world > 1:
+            slack = _half_ulp_bf16(ref)
+            dist.all_reduce(ref); dist.all_reduce(slack)
+        raw, beyond, ref_max = _err_figures(fused, ref, slack)
+        parity = {"err_rel_vs_unfused": raw, "err_beyond_bf16_rounding": beyond, "ref_max": ref_max,
+                  "tol": 8e-3 if wl.kv_mult > 1 else 2e-3, "unfused_attention": lib_name,
+                  "note": "err_rel as in the reference bench (max abs / ref max, both bf16); "
+                          "tol applies beyond the half-ulp a bf16 value carries"}
+        if world > 1:
+            t = torch.tensor([raw, beyond], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            parity["err_rel_vs_unfused"], parity["err_beyond_bf16_rounding"] = (float(x) for x in t)
+        parity["ok"] = bool(parity["err_beyond_bf16_rounding"] <= parity["tol"])
 
     cpu = None
     if rank == 0 and tp == 1 and not args.no_cpu_baseline:
-        v, dt, threads, desc = cpu_chain_sample(wl, tp, 0, max_seconds_hint=args.cpu_seconds)
+        v, dt, threads, desc, chosen, Yp = cpu_chain_sample(wl, tp, 0, max_seconds_hint=args.cpu_seconds)
         cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc,
                "seconds": dt}
+        if parity is not None:
+            fused = ws.output(meta)
+            cq = [0]
+            for a in wl.seqlens_q:
+                cq.append(cq[-1] + a)
+            rows = torch.cat([fused[cq[i]:cq[i + 1]] for i in chosen])
+            raw, beyond, _ = _err_figures(rows, Yp.to(dev))
+            parity["err_rel_vs_cpu_oracle"] = raw
+            parity["err_beyond_bf16_rounding_vs_cpu_oracle"] = beyond
+            parity["cpu_oracle_rows"] = int(rows.shape[0])
+            parity["ok"] = bool(parity["ok"] and beyond <= parity["tol"])
 
     if rank == 0:
+        stage_note = {"fused": "", "fa": " (attention stage only)", "ar": " (AllReduce stage only)",
+                      "oproj": " (O_proj stage only)", "noar": " (no AllReduce)"}[args.stage]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": tp, "steps": K,
             "warmup": W, "ms_per_step": ms_fused, "higher_is_better": True,
             "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": f"{wl.name} tp{tp}" + ("" if args.stage == "fused" else " (attention stage only)"), "seqlens_q": wl.seqlens_q,
+            "config": {"workload": workload_name(wl, tp) + stage_note, "seqlens_q": wl.seqlens_q,
                        "kv_mult": wl.kv_mult, "H_local": h, "H_kv": hkv, "hidden": wl.hidden,
-                       "role_weights": list(w), "sg": cfg.sg, "launch_flags": ws.default_flags,
+                       "role_weights": list(w), "sg": cfg.sg, "launch_flags": flags,
                        "l2": "512 MiB buffer written before every timed launch"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": K,
-            "clocks": clocks, "unfused": unfused,
+            "clocks": clocks, "unfused": unfused, "parity": parity, "scaling_anchor": anchor,
             "allreduce": {"S_bytes": S, "bus_bytes": bus,
                           "bus_gbs": bus / (ms_fused * 1e-3) / 1e9},
         }

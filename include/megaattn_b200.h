@@ -49,6 +49,13 @@ typedef enum ma_error {
                                   multicast path runs far below the NVLink copy rate).  Same sum:
                                   fp32, rounded once.  No reference counterpart. */
 #define MA_FLAG_TILE_ORDER 4u /* claim attention tasks in row-tile order, ignoring fa_order */
+#define MA_FLAG_AR_RIDE 128u  /* tp_size > 1: a ready AllReduce slot of this rank rides along with
+                                 each O_proj task; its reductions are in flight while the compute
+                                 warps wait for the tensor pipe.  Results are bit-identical with
+                                 and without it.  No reference counterpart. */
+/* ma_launch refuses (MA_ERR_INVALID): more than one of FA_ONLY / AR_ONLY / NO_AR / OPROJ_ONLY;
+ * AR_ONLY on one rank or without a multicast address; OPROJ_ONLY with tp_size > 1; AR_P2P unless
+ * tp_size == 2 with both peer_csym set; unknown bits. */
 
 typedef struct ma_devinfo {
   int32_t cc_major, cc_minor, num_sms, max_smem_optin;
@@ -65,7 +72,9 @@ typedef struct ma_devinfo {
  *   csym [max_row_tiles, 128, num_out, 128] bf16 (symmetric across ranks when tp > 1)
  *   ctrl u32[8]  sync_ctrl u32[3]  actv i32[6]  head_ready u32[max_row_tiles]
  *   oproj_queue u32[max_total_oproj]  ready_count u32[max_owner_slots] (symmetric)
- *   ready_bits u64[max_owner_words] (symmetric)  ar_done_bits u64[max_owner_words]
+ *   ready_bits u64[max_owner_words] (symmetric; the reference's ready bitset, kept in the
+ *   descriptor for its buffer list but not read by this kernel: may be 0)
+ *   ar_done_bits u64[max_owner_words]
  *   nvl_signal i32[2] (symmetric)  cu_q, cu_k i32[max_batch+1]  fa_b, fa_mb, fa_order i32[max_row_tiles]
  *   status u32[8]
  * All control buffers must be zero when the plan is first launched.
@@ -177,12 +186,15 @@ void ma_plan_destroy(ma_plan* plan);
  * only rows < valid_m and columns < hidden are written.
  *
  * The first call on a device looks up the array's device address; make that first call
- * outside any stream capture.  Every call uses the same array: it keeps the previous
+ * before any stream capture.  A call on a stream that is being captured is refused with
+ * MA_ERR_INVALID (it copies descriptors from a host buffer that the next call reuses).
+ * Every call uses the same array: it keeps the previous
  * call's contents (what has to start from zero is cleared by the call), and two calls
  * that overlap on the GPU - different streams, or different host threads - race on it.
  * The device must be current.  The call returns once the work is queued on `stream`;
  * if `status_out` is not NULL it instead waits for the stream and fills it, returning
- * MA_ERR_DEVICE_TIMEOUT when a device-side wait gave up.
+ * MA_ERR_DEVICE_TIMEOUT when a device-side wait gave up.  `status_out` is the only way to
+ * learn of such a timeout: the status words sit in the array and no other call reads them.
  */
 #define MA_NOALLOC_OSCRATCH_BYTES (16u << 20)
 #define MA_NOALLOC_CONTROL_BYTES (64u << 10)

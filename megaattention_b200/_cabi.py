@@ -18,6 +18,7 @@ MA_FLAG_AR_ONLY = 8
 MA_FLAG_NO_AR = 16
 MA_FLAG_OPROJ_ONLY = 32
 MA_FLAG_AR_P2P = 64
+MA_FLAG_AR_RIDE = 128
 
 MA_OK = 0
 MA_ERR_INVALID = -1
@@ -86,7 +87,7 @@ def _load():
     path = _build.LIB
     if not os.path.exists(path) or _build._stale():
         try:
-            _build.build()
+            _build.build()     # under a file lock, into a temporary file, then renamed
         except Exception as exc:  # no nvcc on this machine: use what is there, if anything
             if not os.path.exists(path):
                 raise ImportError(f"libmegaattn_b200.so is missing and cannot be built: {exc}")

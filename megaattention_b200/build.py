@@ -23,17 +23,29 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Compile ``csrc/*.cu`` into ``libmegaattn_b200.so`` next to this file."""
     if not force and not _stale():
         return LIB
-    nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
-           "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", LIB]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, f) for f in SOURCES]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        sys.stderr.write(res.stderr)
+    # Several processes (one per GPU under torchrun) may get here at once: one builds, into a
+    # temporary file that is renamed over the library in one step, the others wait on the
+    # lock and find the library fresh.
+    import fcntl
+    with open(LIB + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not _stale():
+            return LIB
+        nvcc = os.environ.get("NVCC", "nvcc")
+        tmp = f"{LIB}.{os.getpid()}.tmp"
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
+               "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", tmp]
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+        cmd += [os.path.join(CSRC, f) for f in SOURCES]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            if os.path.exists(tmp):
+                os.remove(tmp)
+            raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+        os.replace(tmp, LIB)
+        if verbose:
+            sys.stderr.write(res.stderr)
     return LIB
 
 

@@ -170,7 +170,7 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   if (d->hidden < 1 || d->max_row_tiles < 1 || d->max_batch < 1) return MA_ERR_INVALID;
   if (d->max_tot_q < 1 || d->max_tot_k < 1) return MA_ERR_INVALID;
   const uint64_t need[] = {d->Q, d->K, d->V, d->W_o, d->o_scratch, d->csym, d->ctrl, d->sync_ctrl,
-                           d->actv, d->head_ready, d->oproj_queue, d->ready_count, d->ready_bits,
+                           d->actv, d->head_ready, d->oproj_queue, d->ready_count,
                            d->ar_done_bits, d->nvl_signal, d->cu_q, d->cu_k, d->fa_b, d->fa_mb,
                            d->status};
   for (uint64_t a : need) if (a == 0) return MA_ERR_INVALID;
@@ -179,7 +179,7 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   if (d->tp_size > 1) {
     if (d->csym_multicast == 0) return MA_ERR_INVALID;
     for (int r = 0; r < d->tp_size; ++r)
-      if (!d->peer_ready_count[r] || !d->peer_ready_bits[r] || !d->peer_nvl_signal[r])
+      if (!d->peer_ready_count[r] || !d->peer_nvl_signal[r])
         return MA_ERR_INVALID;
   }
 
@@ -219,7 +219,6 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   k.head_ready = reinterpret_cast<uint32_t*>(d->head_ready);
   k.oproj_queue = reinterpret_cast<uint32_t*>(d->oproj_queue);
   k.ready_count = reinterpret_cast<uint32_t*>(d->ready_count);
-  k.ready_bits = reinterpret_cast<unsigned long long*>(d->ready_bits);
   k.ar_done_bits = reinterpret_cast<unsigned long long*>(d->ar_done_bits);
   k.nvl_signal = reinterpret_cast<int*>(d->nvl_signal);
   k.cu_q = reinterpret_cast<const int*>(d->cu_q);
@@ -234,7 +233,6 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   k.csym_mc = d->csym_multicast;
   for (int r = 0; r < MA_MAX_TP; ++r) {
     k.peer_rc[r] = d->peer_ready_count[r];
-    k.peer_rb[r] = d->peer_ready_bits[r];
     k.peer_nvl[r] = d->peer_nvl_signal[r];
     k.peer_csym[r] = d->peer_csym[r];
   }
@@ -257,13 +255,23 @@ int ma_launch(ma_plan* pl, const ma_launch_args* a, void* stream) {
   kp.w_fa = a->w_fa; kp.w_oproj = a->w_oproj;
   kp.w_ar = (kp.tp > 1) ? a->w_ar : 0;          // one rank: no AllReduce role
   kp.flags = a->flags;
+  // Flag combinations that would send the kernel down a path its buffers do not back are
+  // refused here, before anything is launched.
+  const uint32_t stage = kp.flags & (MA_FLAG_FA_ONLY | MA_FLAG_AR_ONLY | MA_FLAG_NO_AR |
+                                     MA_FLAG_OPROJ_ONLY);
+  if (stage & (stage - 1u)) return MA_ERR_INVALID;              // at most one stage selector
+  if ((kp.flags & MA_FLAG_AR_ONLY) && (kp.tp < 2 || kp.csym_mc == 0)) return MA_ERR_INVALID;
+  if ((kp.flags & MA_FLAG_OPROJ_ONLY) && kp.tp != 1) return MA_ERR_INVALID;
   if ((kp.flags & MA_FLAG_AR_P2P) &&
       (kp.tp != 2 || !pl->desc.peer_csym[0] || !pl->desc.peer_csym[1]))
+    return MA_ERR_INVALID;
+  if (kp.flags & ~(MA_FLAG_FA_ONLY | MA_FLAG_DRAIN_FIRST | MA_FLAG_TILE_ORDER | MA_FLAG_AR_ONLY |
+                   MA_FLAG_NO_AR | MA_FLAG_OPROJ_ONLY | MA_FLAG_AR_P2P | MA_FLAG_AR_RIDE))
     return MA_ERR_INVALID;
   if (kp.w_fa < 0 || kp.w_oproj < 0 || kp.w_ar < 0 || kp.w_fa + kp.w_oproj + kp.w_ar < 1)
     return MA_ERR_INVALID;
   int n = a->num_ctas > 0 ? a->num_ctas : pl->num_sms;
-  if (n > pl->num_sms) n = pl->num_sms;          // grid barrier needs every CTA resident
+  if (n > pl->num_sms) n = pl->num_sms;          // one CTA per SM: every CTA must be resident (CTAs wait on each other's work)
   cudaError_t e = ma::launch_fused_prefill(pl->maps, kp, n, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? MA_OK : MA_ERR_CUDA;
 }

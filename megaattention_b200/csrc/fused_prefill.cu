@@ -5,19 +5,30 @@
 // src/mega_attention/kernels/sm90/fused_fa_oproj_ar.py:148-398):
 //   FA task    (row_tile, q head[s])  : S = Q K^T and O += P V as tcgen05 MMAs with fp32
 //                                       accumulators in TMEM, online softmax by one thread
-//                                       per row, result to O_scratch (bf16)
-//   O_proj task (row_tile, n super-group): C[128, <=512] = O_scratch tile @ W_o columns,
-//                                       one TMEM accumulator of up to 512 columns so the
-//                                       A tile streams once per super-group
+//                                       per row, result to O_scratch (bf16) by TMA store
+//   O_proj task (row_tile, n super-group): C[128, <=512] = O_scratch tile @ W_o columns in
+//                                       two passes of 256 columns, each into one of two
+//                                       ping-pong TMEM accumulators, so a pass's epilogue
+//                                       runs under the next pass's MMAs (the A tile
+//                                       streams once per pass)
 //   AR task    (owned slot)           : multimem.ld_reduce / multimem.st over the NVLS
-//                                       multicast view of the symmetric output
+//                                       multicast view of the symmetric output (or plain
+//                                       peer loads / stores with two ranks); an owned slot
+//                                       can also ride along with an O_proj task, its
+//                                       reductions in flight while the tensor pipe works
 //
-// Warp roles (12 warps): warp 0 = scheduler + TMA producer, warp 1 = MMA issuer (and TMEM
-// allocator), warps 2-3 = extra AllReduce lanes, warps 4-7 / 8-11 = two compute
-// warpgroups (softmax + epilogues).  When q heads come in pairs that share a kv head, an
-// FA task is two q heads of one row tile: both tiles use the same K/V stages and the two
-// compute warpgroups alternate, so the tensor pipe runs one tile's MMAs under the other
-// tile's softmax.
+// Warp roles (12 warps, 384 threads):
+//   warp 0 (lane 0)  TMA producer: Q tiles, the K/V ring, O_proj stages
+//   warp 1 (lane 0)  MMA issuer of attention tile 0 and of every O_proj task; warp 1 also
+//                    allocates and frees TMEM
+//   warp 2 (lane 0)  scheduler: claims tasks, fills one of two descriptor slots, publishes
+//                    completions (runs one task ahead of the workers)
+//   warp 3 (lane 0)  MMA issuer of attention tile 1
+//   warps 4-7, 8-11  two compute warpgroups: online softmax (one thread per row), both
+//                    epilogues, AllReduce slots
+// When q heads come in pairs that share a kv head, an FA task is two q heads of one row
+// tile: both tiles use the same K/V stages and the two compute warpgroups alternate, so
+// the tensor pipe runs one tile's MMAs under the other tile's softmax.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -60,27 +71,12 @@ struct Bars {
   uint64_t acc_full[2];     // MMA: O_proj accumulator half h complete
   uint64_t acc_free[2];     // epilogue warps: half h read out (count 8)
   uint64_t drain[2];        // abort path only: an issuer's outstanding MMAs have retired
-  uint64_t dbg;             // trace builds only
 };
 
 struct Env {
   const KParams* p;
   volatile int* abort_flag;
 };
-
-// Optional event trace (compiled in with -DMA_TRACE only): CTA 0 stamps (code, clock) pairs
-// per role into the words that follow the 8 status words.
-#ifdef MA_TRACE_FINE
-#define MA_TRACE_DECL(role_id) uint32_t tr_n = 0; const int tr_role = (role_id);
-#define MA_EV(code)                                                                        \
-  if (blockIdx.x == 0 && tr_n < 1000) {                                                    \
-    uint32_t* tb = p.status + 8 + tr_role * 2048 + tr_n * 2;                               \
-    tb[0] = (code); tb[1] = static_cast<uint32_t>(clock64()); ++tr_n;                      \
-  }
-#else
-#define MA_TRACE_DECL(role_id)
-#define MA_EV(code)
-#endif
 
 __device__ __noinline__ void report(const Env& e, uint32_t code, uint32_t site, uint32_t aux) {
   if (atomicCAS(e.p->status, 0u, code) == 0u) {
@@ -159,7 +155,8 @@ __device__ __forceinline__ bool try_pop_oproj(const KParams& p, int total_op, in
 // fire-and-forget adds on the owner's ready_count; a slot is ready when its count equals
 // tp, and the owner's CTAs each watch their own stretch of the count array (plus a few
 // neighbours', and now and then all of it), claiming with a compare-and-swap that marks the
-// count.  ready_bits is no longer used.
+// count.  The reference's ready bitset has no role here (the plan descriptor still has
+// the field so that the workspace keeps the reference's buffer list; it may be 0).
 constexpr uint32_t kArClaimed = 0x40000000u;
 __device__ __forceinline__ bool try_claim_ar(const KParams& p, int local_owned, uint32_t poll_no,
                                              int* arg) {
@@ -210,16 +207,6 @@ __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, i
     if (static_cast<int>(ld_relaxed_gpu(p.ctrl + C_AR_CURSOR)) < local_owned) {
       const int idx = static_cast<int>(atom_add_relaxed_gpu(p.ctrl + C_AR_CURSOR, 1u));
       if (idx < local_owned) { *mode = MODE_AR; *arg = idx * p.tp + p.rank; }
-    }
-    return;
-  }
-  if (p.flags & 32u) {
-    // O_proj-only launch (single rank): O_scratch is taken as complete, slots are handed
-    // out in order by the consume counter
-    if (static_cast<int>(ld_acquire_gpu(p.ctrl + C_OP_DONE)) >= total_op) { *mode = MODE_DONE; return; }
-    if (static_cast<int>(ld_relaxed_gpu(p.ctrl + C_OP_CONSUME)) < total_op) {
-      const int t = static_cast<int>(atom_add_relaxed_gpu(p.ctrl + C_OP_CONSUME, 1u));
-      if (t < total_op) { *mode = MODE_OPROJ; *arg = t; }
     }
     return;
   }
@@ -384,66 +371,79 @@ __device__ __forceinline__ void stage_row32(uint32_t panel, int row, int col0,
   }
 }
 
-// One AllReduce slot: 128 rows x (vnt x 128) bf16 columns, reduced in the switch and
-// written back to every rank.  `nthr` threads cooperate; each keeps U 16-byte reductions in
-// flight before its first store (NVLink round trips are microseconds).
-template <int U>
-__device__ __forceinline__ void ar_batch(const KParams& p, int ft, int base_out, int c0, int nthr) {
-  auto chunk_addr = [&](int c) -> unsigned long long {
-    const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
-    const size_t elem =
-        ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
-    return p.csym_mc + elem * 2;
-  };
-  uint4 v[U];
-#pragma unroll
-  for (int u = 0; u < U; ++u) v[u] = multimem_ld_reduce_bf16x8(chunk_addr(c0 + u * nthr));
-#pragma unroll
-  for (int u = 0; u < U; ++u) multimem_st_b128(chunk_addr(c0 + u * nthr), v[u]);
+// ---------------------------------------------------------------- AllReduce of one slot
+// A slot is 128 rows x (vnt x 128) bf16 columns = vnt x 2048 chunks of 16 bytes.  The 256
+// compute threads walk it in batches; a batch is split into its loads (ar_load: up to 16
+// 16-byte requests per thread go out, nothing waits) and its stores (ar_store: the first
+// use of the loaded registers, i.e. where the thread waits for the round trip), so the
+// caller can put other work between the two.
+//   multimem path: 16 (or, for the last odd column tile, 8) multimem.ld_reduce per thread
+//     (fp32 sum of all ranks' bf16 taken in the switch), then multimem.st to every rank;
+//   peer path (MA_FLAG_AR_P2P, two ranks): 8 chunks per thread, the peer's and this rank's
+//     partial loaded with plain 16-byte loads, added in fp32, rounded once, written to both
+//     copies.  With two GPUs the multicast path runs far below the NVLink copy rate.
+constexpr int kArThreads = 256;
+struct ArCursor {
+  int ft, base_out, c0, total;     // c0: this thread's first chunk of the next batch
+};
+__device__ __forceinline__ size_t ar_chunk_elem(const KParams& p, const ArCursor& a, int c) {
+  const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
+  return ((static_cast<size_t>(a.ft * 128 + m) * p.num_out + a.base_out + o_t) * 128) + nc * 8;
 }
-
-// The same batch with plain peer loads and stores, two ranks only: the owner reads its own
-// and the peer's partial, adds in fp32, rounds once and writes both copies.  With two GPUs
-// the multicast path is several times slower than the NVLink copy rate; this one is not.
-template <int U>
-__device__ __forceinline__ void ar_batch_p2p(const KParams& p, int ft, int base_out, int c0, int nthr) {
-  auto chunk_off = [&](int c) -> unsigned long long {
-    const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
-    const size_t elem =
-        ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
-    return elem * 2;
-  };
-  const unsigned long long mine = p.peer_csym[p.rank], peer = p.peer_csym[p.rank ^ 1];
-  uint4 a[U], b[U];
+// Chunks per thread of the next batch: 16 / 8 / 0 (multimem), 8 / 0 (peer path).
+__device__ __forceinline__ int ar_batch_n(const KParams& p, const ArCursor& a) {
+  if (!(p.flags & 64u) && a.c0 + kArThreads * 15 < a.total) return 16;
+  return (a.c0 + kArThreads * 7 < a.total) ? 8 : 0;
+}
+__device__ __forceinline__ void ar_load(const KParams& p, const ArCursor& a, int n, uint4 (&v)[16]) {
+  if (p.flags & 64u) {
+    const unsigned long long mine = p.peer_csym[p.rank], peer = p.peer_csym[p.rank ^ 1];
 #pragma unroll
-  for (int u = 0; u < U; ++u) b[u] = ld_relaxed_sys_b128(peer + chunk_off(c0 + u * nthr));
+    for (int u = 0; u < 8; ++u)
+      v[u] = ld_relaxed_sys_b128(peer + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2);
 #pragma unroll
-  for (int u = 0; u < U; ++u) a[u] = ld_relaxed_sys_b128(mine + chunk_off(c0 + u * nthr));
+    for (int u = 0; u < 8; ++u)
+      v[8 + u] = ld_relaxed_sys_b128(mine + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2);
+  } else if (n == 16) {
 #pragma unroll
-  for (int u = 0; u < U; ++u) {
-    uint4 r;
-    r.x = add_bf16x2_via_f32(a[u].x, b[u].x); r.y = add_bf16x2_via_f32(a[u].y, b[u].y);
-    r.z = add_bf16x2_via_f32(a[u].z, b[u].z); r.w = add_bf16x2_via_f32(a[u].w, b[u].w);
-    const unsigned long long off = chunk_off(c0 + u * nthr);
-    st_relaxed_sys_b128(peer + off, r);
-    st_relaxed_sys_b128(mine + off, r);
+    for (int u = 0; u < 16; ++u)
+      v[u] = multimem_ld_reduce_bf16x8(p.csym_mc + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2);
+  } else {
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      v[u] = multimem_ld_reduce_bf16x8(p.csym_mc + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2);
   }
 }
-
-// One AllReduce slot: 128 rows x (vnt x 128) bf16 columns, reduced in the switch and
-// written back to every rank.  `nthr` (256) threads cooperate; each keeps 16 16-byte
-// reductions in flight before its first store (NVLink round trips are microseconds).  A
-// slot is vnt x 2048 chunks: whole batches of nthr x 16, then one of nthr x 8 if vnt is odd.
-__device__ __forceinline__ void ar_slot(const KParams& p, int ft, int base_out, int vnt, int t,
-                                        int nthr) {
-  const int total = vnt * 2048;
-  int c0 = t;
-  if (p.flags & 64u) {      // MA_FLAG_AR_P2P (host side admits it at tp == 2 only)
-    for (; c0 + nthr * 7 < total; c0 += nthr * 8) ar_batch_p2p<8>(p, ft, base_out, c0, nthr);
-    return;
+__device__ __forceinline__ void ar_store(const KParams& p, ArCursor& a, int n, const uint4 (&v)[16]) {
+  if (p.flags & 64u) {
+    const unsigned long long mine = p.peer_csym[p.rank], peer = p.peer_csym[p.rank ^ 1];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      uint4 r;
+      r.x = add_bf16x2_via_f32(v[8 + u].x, v[u].x); r.y = add_bf16x2_via_f32(v[8 + u].y, v[u].y);
+      r.z = add_bf16x2_via_f32(v[8 + u].z, v[u].z); r.w = add_bf16x2_via_f32(v[8 + u].w, v[u].w);
+      const unsigned long long off = ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2;
+      st_relaxed_sys_b128(peer + off, r);
+      st_relaxed_sys_b128(mine + off, r);
+    }
+  } else if (n == 16) {
+#pragma unroll
+    for (int u = 0; u < 16; ++u)
+      multimem_st_b128(p.csym_mc + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2, v[u]);
+  } else {
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      multimem_st_b128(p.csym_mc + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2, v[u]);
   }
-  for (; c0 + nthr * 15 < total; c0 += nthr * 16) ar_batch<16>(p, ft, base_out, c0, nthr);
-  if (c0 + nthr * 7 < total) ar_batch<8>(p, ft, base_out, c0, nthr);
+  a.c0 += kArThreads * n;
+}
+// Whatever is left of a slot, batch after batch.
+__device__ __forceinline__ void ar_rest(const KParams& p, ArCursor& a) {
+  uint4 v[16];
+  for (int n = ar_batch_n(p, a); n > 0; n = ar_batch_n(p, a)) {
+    ar_load(p, a, n, v);
+    ar_store(p, a, n, v);
+  }
 }
 
 }  // namespace
@@ -452,7 +452,9 @@ __device__ __forceinline__ void ar_slot(const KParams& p, int ft, int base_out, 
 enum : int { T_MODE = 0, T_FT = 1,
              TF_HEAD0 = 2, TF_NT = 3, TF_KVH = 4, TF_QROW0 = 5, TF_VALID = 6, TF_KSTART = 7,
              TF_KLEN = 8, TF_OFFSET = 9, TF_NBLK = 10, TF_MB = 11,
-             TO_BASE = 2, TO_VNT = 3, TO_VALID = 4, TO_SLOT = 5, T_WORDS = 12 };
+             TO_BASE = 2, TO_VNT = 3, TO_VALID = 4, TO_SLOT = 5,
+             // an owned AllReduce slot riding along with an O_proj task (TO_AR_SLOT < 0: none)
+             TO_AR_SLOT = 6, TO_AR_FT = 7, TO_AR_BASE = 8, TO_AR_VNT = 9, T_WORDS = 12 };
 
 __device__ __forceinline__ bool is_tile_mode(int m) { return m == MODE_FA || m == MODE_OPROJ; }
 
@@ -503,7 +505,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     }
     mbar_init(smem_u32(&bars.drain[0]), 1);
     mbar_init(smem_u32(&bars.drain[1]), 1);
-    mbar_init(smem_u32(&bars.dbg), 1);
     fence_mbar_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -520,7 +521,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
 
   // Every role walks the two descriptor slots in turn.  A role arrives on task_empty[k]
   // when its part of the task in slot k is finished; the scheduler publishes the task's
-  // completion and refills the slot once all ten arrivals are in, so the scheduler runs
+  // completion and refills the slot once all eleven arrivals are in (producer, two MMA
+  // issuers, eight compute warps), so the scheduler runs
   // one task ahead of the workers.  Attention tiles and O_proj tiles overlay the same
   // shared memory and TMEM: a role that goes from one kind to the other first waits for
   // the previous task to finish completely (same-kind neighbours overlap freely).
@@ -563,7 +565,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       bool ld_pending[2] = {false, false}, ld_skip[2] = {false, false};
       int pending_ticket = -1;
       uint32_t poll_no = 0;
-      int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0};
+      int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0}, occ_ride[2] = {-1, -1};
+      const bool ar_ride = p.tp > 1 && (p.flags & 128u) && !(p.flags & (1u | 8u | 16u | 32u));
       auto publish = [&](int kk) {
         if (s_abort) return;
         if (occ_mode[kk] == MODE_FA) {
@@ -575,6 +578,10 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           atom_add_release_gpu(p.ctrl + C_FA_DONE, static_cast<uint32_t>(occ_b[kk]));
         } else if (occ_mode[kk] == MODE_OPROJ) {
           publish_ar_ready(p, occ_a[kk]);
+          if (occ_ride[kk] >= 0) {        // the slot that rode along is reduced as well
+            finish_ar_slot(p, occ_ride[kk]);
+            occ_ride[kk] = -1;
+          }
         } else if (occ_mode[kk] == MODE_AR) {
           fence_acq_rel_sys();
           finish_ar_slot(p, occ_a[kk]);
@@ -652,6 +659,18 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           d[T_FT] = ft; d[TO_BASE] = base_out; d[TO_VNT] = min(p.sg, p.num_out - base_out);
           d[TO_VALID] = min(128, q_len - mb * 128); d[TO_SLOT] = arg;
           occ_a[k] = arg;
+          d[TO_AR_SLOT] = -1;
+          if (mode == MODE_OPROJ && ar_ride) {
+            // The compute warps of an O_proj task mostly wait for the tensor pipe: give
+            // them a ready AllReduce slot of this rank to reduce meanwhile.
+            int ar_arg;
+            if (try_claim_ar(p, local_owned, poll_no++, &ar_arg)) {
+              const int aft = ar_arg / p.nsg, ag = ar_arg % p.nsg;
+              d[TO_AR_SLOT] = ar_arg; d[TO_AR_FT] = aft; d[TO_AR_BASE] = ag * p.sg;
+              d[TO_AR_VNT] = min(p.sg, p.num_out - ag * p.sg);
+              occ_ride[k] = ar_arg;
+            }
+          }
         }
         d[T_MODE] = mode;
         occ_mode[k] = mode;
@@ -667,14 +686,17 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     } else if (warp == 0 && lane == 0) {
       // ==================================================================== TMA producer
       uint32_t kv_slot = 0, kv_ph = 0, opc = 0, q_uses[2] = {0, 0};
-      MA_TRACE_DECL(0)
       while (true) {
         MA_NEXT_TASK(d, mode)
         MA_DRAIN_IF_SWITCH(mode)
         if (mode == MODE_FA) {
           const int nt = d[TF_NT], nblk = d[TF_NBLK];
-          for (int i = 0; i < nt; ++i) {
-            wait_bar(env, smem_u32(&bars.q_empty[i]), (q_uses[i] & 1u) ^ 1u, 0x18 + i);
+          // a wait that gave up (abort) ends the task's loads: nothing is written into a
+          // buffer that was not waited for
+          bool ok = true;
+          for (int i = 0; i < nt && ok; ++i) {
+            ok = wait_bar(env, smem_u32(&bars.q_empty[i]), (q_uses[i] & 1u) ^ 1u, 0x18 + i);
+            if (!ok) break;
             ++q_uses[i];
             const uint32_t bar = smem_u32(&bars.q_full[i]);
             mbar_expect_tx(bar, kTile);
@@ -682,14 +704,14 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           }
           const int kvh = d[TF_KVH];
           const int k_base = d[TF_KSTART];
-          for (int jj = 0; jj < nblk; ++jj) {
+          for (int jj = 0; jj < nblk && ok; ++jj) {
             const int blk = nblk - 1 - jj;
             // key block -> first row of its 128-row tile (paged: one page is one block)
             const int kv_row = p.page_table ? p.page_table[k_base + blk] * 128 : k_base + blk * 128;
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
-              wait_bar(env, smem_u32(&bars.kv_empty[kv_slot]), kv_ph ^ 1u, 0x10 + kv_slot);
-              MA_EV(60 + which)
+              if (!ok || !(ok = wait_bar(env, smem_u32(&bars.kv_empty[kv_slot]), kv_ph ^ 1u, 0x10 + kv_slot)))
+                break;
               const uint32_t bar = smem_u32(&bars.kv_full[kv_slot]);
               mbar_expect_tx(bar, kTile);
               tma_load_4d(smem0 + kSmKV + kv_slot * kTile, which ? &tmV : &tmK, bar, 0, kv_row, 0, kvh);
@@ -699,16 +721,17 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         } else if (mode == MODE_OPROJ) {
           const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT];
           const int nkc = p.K_local >> 6;
-          fence_proxy_async_global();   // O_scratch was written with ordinary stores
-          for (int h = 0; h * 2 < vnt; ++h) {
+          fence_proxy_async_global();   // O_scratch was written by other CTAs' TMA stores
+          bool ok = true;
+          for (int h = 0; h * 2 < vnt && ok; ++h) {
             for (int kc = 0; kc < nkc; ++kc) {
               const uint32_t st = opc & 3u;
-              wait_bar(env, smem_u32(&bars.op_empty[st]), ((opc >> 2) & 1u) ^ 1u, 0x90 + st);
+              ok = wait_bar(env, smem_u32(&bars.op_empty[st]), ((opc >> 2) & 1u) ^ 1u, 0x90 + st);
+              if (!ok) break;
               const uint32_t bar = smem_u32(&bars.op_full[st]);
               const uint32_t a_dst = smem0 + st * kOpStage;
               // A chunk 128 x 64 and a W slab of 64 k x 256 n (4 panels; panels past the
               // padded width are filled with zeros)
-              MA_EV(62)
               mbar_expect_tx(bar, kPanel + 4u * kWPanel);
               tma_load_2d(a_dst, &tmO, bar, kc * 64, ft * 128);
               tma_load_3d(a_dst + kPanel, &tmW, bar, 0, kc * 64, (base_out + 2 * h) * 2);
@@ -737,7 +760,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           if (atomicCAS(&s_pipe_turn, 0, 1) == 0) return;
       };
       auto pipe_unlock = [&]() { atomicExch(&s_pipe_turn, 0); };
-      MA_TRACE_DECL(mi == 0 ? 1 : 10)
       while (true) {
         MA_NEXT_TASK(d, mode)
         MA_DRAIN_IF_SWITCH(mode)
@@ -764,7 +786,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             const uint32_t slot_v = kv_slot;
             wait_bar(env, smem_u32(&bars.kv_full[slot_v]), kv_ph, 0x40 + slot_v);
             if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
-            MA_EV(12)
             if (act) {
               if (jj == 0) {   // the previous task's epilogue must have read O out
                 wait_bar(env, smem_u32(&bars.o_free[mi]), (o_uses & 1u) ^ 1u, 0x68 + mi);
@@ -772,7 +793,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
               }
               wait_bar(env, smem_u32(&bars.p_full[mi]), p_par, 0x60 + mi);
               p_par ^= 1u;
-              MA_EV(10)
               tc_fence_after();
             }
             const bool has_next = (jj + 1 < nblk);
@@ -781,17 +801,14 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
               wait_bar(env, smem_u32(&bars.kv_full[slot_kk]), kv_ph, 0x50 + slot_kk);
               if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
             }
-            MA_EV(13)
             if (act) {
               pipe_lock();
-              MA_EV(14)
               issue_pv(t_o, t_s, smem0 + kSmKV + slot_v * kTile, jj > 0);
               tc_commit(smem_u32(&bars.kv_empty[slot_v]));
               if (has_next) {
                 issue_qk(t_s, sm_q, smem0 + kSmKV + slot_kk * kTile);
                 tc_commit(smem_u32(&bars.s_full[mi]));
                 pipe_unlock();
-                MA_EV(20)
                 tc_commit(smem_u32(&bars.kv_empty[slot_kk]));
                 if (jj + 2 == nblk) tc_commit(smem_u32(&bars.q_empty[mi]));
               } else {
@@ -809,15 +826,12 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           for (int h = 0; h * 2 < vnt; ++h) {
             const int ncols = min(2, vnt - 2 * h) * 128;
             const uint32_t idesc = make_idesc_bf16(128, ncols, 0, 1);
-            MA_EV(42)
             wait_bar(env, smem_u32(&bars.acc_free[h]), (acc_uses[h] & 1u) ^ 1u, 0xA8 + h);
             ++acc_uses[h];
-            MA_EV(43)
             for (int kc = 0; kc < nkc; ++kc) {
               const uint32_t st = opc & 3u;
               wait_bar(env, smem_u32(&bars.op_full[st]), (opc >> 2) & 1u, 0xA0 + st);
               ++opc;
-              MA_EV(40)
               tc_fence_after();
               const uint32_t a16 = (smem0 + st * kOpStage) >> 4;
               const uint32_t w16 = a16 + (kPanel >> 4);
@@ -829,7 +843,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
               tc_commit(smem_u32(&bars.op_empty[st]));
             }
             tc_commit(smem_u32(&bars.acc_full[h]));
-            MA_EV(41)
           }
         }
         MA_TASK_DONE(mode)
@@ -843,24 +856,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     const int row = (warp & 3) * 32 + lane;                    // TMEM lane == tile row
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t s_par = 0, o_par = 0, acc_par[2] = {0, 0};
-    MA_TRACE_DECL(2 + (warp - 4))
-#ifdef MA_TRACE
-    long long acct[4] = {0, 0, 0, 0};   // idle, FA, O_proj, AR cycles of this CTA
-    int acct_n[4] = {0, 0, 0, 0};
-    long long t_mark = clock64();
-    int tl_n = 0;
-    uint32_t* tl = p.status + 8 + 11 * 2048 + 148 * 8 + blockIdx.x * 128;
-#endif
     while (true) {
       MA_NEXT_TASK(d, mode)
-#ifdef MA_TRACE
-      { const long long now = clock64(); acct[0] += now - t_mark; t_mark = now; }
-      if (warp == 4 && lane == 0 && tl_n < 31) {
-        tl[tl_n * 4 + 0] = static_cast<uint32_t>(globaltimer_ns());
-        tl[tl_n * 4 + 2] = mode; tl[tl_n * 4 + 3] = d[T_FT] * 1000 + (mode == MODE_FA ? d[TF_NBLK] : d[TO_BASE]);
-      }
-#endif
-      if (lane == 0) { MA_EV(1000 + mode) }
       if (mode == MODE_FA && wg < d[TF_NT]) {
         // -------------------------------------------- softmax + epilogue of tile `wg`
         const int ft = d[T_FT], head = d[TF_HEAD0] + wg, valid_m = d[TF_VALID];
@@ -878,13 +875,11 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           const int j = nblk - 1 - jj;
           wait_bar(env, bar_s, s_par, 0x70 + wg);
           s_par ^= 1u;
-          if (lane == 0) { MA_EV(30) }
           tc_fence_after();
           uint32_t s[4][32];
 #pragma unroll
           for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
           tc_wait_ld();
-          if (lane == 0) { MA_EV(31) }
           const bool need_mask = ((j + 1) * 128 - 1 > mb * 128 + offset) || ((j + 1) * 128 > k_len);
           if (need_mask) {
             const int lim = lim_abs - j * 128;    // columns > lim are masked
@@ -979,7 +974,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
                 tmem_st32(t_o + c * 32, o);
               }
             }
-            if (lane == 0) { MA_EV(32) }
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * sl2;
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -1004,17 +998,14 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             }
             l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
           }
-          if (lane == 0) { MA_EV(33) }
           tc_wait_st();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_p);   // 4 arrivals, not 128 serialised ones
-          if (lane == 0) { MA_EV(34) }
         }
         // epilogue: O / l -> bf16 -> O_scratch[ft, row, head, :]; tail rows are zeros
         wait_bar(env, smem_u32(&bars.o_done[wg]), o_par, 0x80 + wg);
         o_par ^= 1u;
-        if (lane == 0) { MA_EV(35) }
         tc_fence_after();
         const float inv = (row < valid_m && l_run > 0.f) ? (1.f / l_run) : 0.f;
         // O / l -> bf16 -> this tile's Q buffer (free: every Q K^T of the task is done),
@@ -1046,15 +1037,21 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           fence_proxy_async_all();     // O_scratch is read back by TMA loads of other CTAs
           __threadfence();
         }
-        if (lane == 0) { MA_EV(36) }
       } else if (mode == MODE_OPROJ) {
         const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT], valid_m = d[TO_VALID];
         const bool leader = ((warp & 3) == 0 && lane == 0);
         const uint32_t stg = smem0 + kSmOpStaging + wg * kPanel;   // [128 rows][64 cols] bf16
+        // An AllReduce slot riding along: one batch of reductions goes out before each wait
+        // for an accumulator and is stored after that pass's epilogue, so the NVLink round
+        // trips pass while the tensor pipe works; what is left is done after the last pass.
+        ArCursor arc{d[TO_AR_FT], d[TO_AR_BASE], tid - 128, 0};
+        if (d[TO_AR_SLOT] >= 0) arc.total = d[TO_AR_VNT] * 2048;
+        uint4 arv[16];
         for (int h = 0; h * 2 < vnt; ++h) {
+          const int ar_n = ar_batch_n(p, arc);
+          if (ar_n) ar_load(p, arc, ar_n, arv);
           wait_bar(env, smem_u32(&bars.acc_full[h]), acc_par[h], 0xB0 + h);
           acc_par[h] ^= 1u;
-          if (lane == 0) { MA_EV(50 + h) }
           tc_fence_after();
           const int o_t = 2 * h + wg;                   // column tile inside the super-group
           if (o_t < vnt) {
@@ -1114,6 +1111,11 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars.acc_free[h]));
           }
+          if (ar_n) ar_store(p, arc, ar_n, arv);
+        }
+        if (arc.total) {
+          ar_rest(p, arc);
+          if (lane == 0) __threadfence_system();   // one per warp; the scheduler fences again
         }
         // Ordering towards other CTAs / ranks: the leader waits for its TMA stores, rows
         // written directly get a gpu-scope fence; the one system-scope fence per task is
@@ -1124,28 +1126,16 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           fence_proxy_async_all();
         }
         if (valid_m != 128) __threadfence();
-        if (lane == 0) { MA_EV(52) }
       } else if (mode == MODE_AR) {
-        const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT];
-        const int ctid = tid - 128;
-        ar_slot(p, ft, base_out, vnt, ctid, 256);
+        ArCursor arc{d[T_FT], d[TO_BASE], tid - 128, d[TO_VNT] * 2048};
+        ar_rest(p, arc);
         if (lane == 0) __threadfence_system();   // one per warp; the scheduler fences again
       }
       __syncwarp();
-#ifdef MA_TRACE
-      { const long long now = clock64(); acct[mode] += now - t_mark; acct_n[mode]++; t_mark = now; }
-      if (warp == 4 && lane == 0 && tl_n < 31) { tl[tl_n * 4 + 1] = static_cast<uint32_t>(globaltimer_ns()); ++tl_n; }
-#endif
       if (lane == 0) mbar_arrive(smem_u32(&bars.task_empty[slot_k]));
       ++n_arrived[slot_k];
       prev_mode = mode; prev_k = slot_k; slot_k ^= 1;
     }
-#ifdef MA_TRACE
-    if (warp == 4 && lane == 0) {
-      uint32_t* ab = p.status + 8 + 11 * 2048 + blockIdx.x * 8;
-      for (int i = 0; i < 4; ++i) { ab[i] = static_cast<uint32_t>(acct[i]); ab[4 + i] = acct_n[i]; }
-    }
-#endif
   }
 #undef MA_NEXT_TASK
 #undef MA_DRAIN_IF_SWITCH
@@ -1169,7 +1159,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     if (s_last) {
       for (int i = tid; i < p.max_row_tiles; i += kThreads) p.head_ready[i] = 0u;
       for (int i = tid; i < p.max_owner_slots; i += kThreads) p.ready_count[i] = 0u;
-      for (int i = tid; i < p.max_owner_words; i += kThreads) { p.ready_bits[i] = 0ull; p.ar_done_bits[i] = 0ull; }
+      for (int i = tid; i < p.max_owner_words; i += kThreads) p.ar_done_bits[i] = 0ull;
       if (tid < 8) p.ctrl[tid] = 0u;
       if (tid == 8) p.sync_ctrl[S_GS_QUIESCE] = 0u;
       __threadfence_system();

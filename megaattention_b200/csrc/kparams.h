@@ -39,7 +39,6 @@ struct KParams {
   uint32_t* head_ready;
   uint32_t* oproj_queue;
   uint32_t* ready_count;
-  unsigned long long* ready_bits;
   unsigned long long* ar_done_bits;
   int* nvl_signal;
   const int* cu_q;
@@ -54,7 +53,6 @@ struct KParams {
 
   unsigned long long csym_mc;
   unsigned long long peer_rc[kMaxTp];
-  unsigned long long peer_rb[kMaxTp];
   unsigned long long peer_nvl[kMaxTp];
   unsigned long long peer_csym[kMaxTp];   // every rank's C_sym (peer-load AllReduce, tp 2)
 };

@@ -1,7 +1,8 @@
 // ma_fused_prefill_noalloc: the fused prefill for callers that may not allocate device
 // memory.  All scratch the kernel needs sits in one file-scope device array; see the
 // declaration in include/megaattn_b200.h for who this is for, the limits and the rules
-// (first call outside stream capture; calls share the array, overlapping calls race).
+// (first call before any stream capture; a capturing stream is refused; calls share the
+// array, overlapping calls race).
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -107,15 +108,22 @@ extern "C" int ma_fused_prefill_noalloc(const ma_noalloc_args* a, void* stream_)
   actv[5] = static_cast<int32_t>(total); actv[6] = 0; actv[7] = 0;
   const size_t meta_ints = 8 + 2 * static_cast<size_t>(B + 1) + 2 * static_cast<size_t>(R);
 
-  // ---- the scratch array's device address (set-up on the first call per device)
+  // ---- the device, then the scratch array's device address (set-up on the first call
+  //      per device)
+  int dev = 0, cc = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return MA_ERR_CUDA;
+  if (cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+    return MA_ERR_CUDA;
+  if (cc != 10) return MA_ERR_NOT_SM100;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // The call copies this call's descriptors from a host buffer it reuses and, with
+  // status_out, synchronises the stream: a stream that is being captured is refused.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) return MA_ERR_CUDA;
+  if (cap != cudaStreamCaptureStatusNone) return MA_ERR_INVALID;
   unsigned char* scr = nullptr;
   int rc = scratch_for_current_device(&scr);
   if (rc != MA_OK) return rc;
-  int dev = 0, cc = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev);
-  if (cc != 10) return MA_ERR_NOT_SM100;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
 
   // ---- clear what must start at zero, then bring in this call's descriptors
   if (cudaMemsetAsync(scr, 0, MA_NOALLOC_CONTROL_BYTES, stream) != cudaSuccess) return MA_ERR_CUDA;
@@ -151,7 +159,6 @@ extern "C" int ma_fused_prefill_noalloc(const ma_noalloc_args* a, void* stream_)
   k.fa_mb = k.fa_b + R;
   k.head_ready = reinterpret_cast<uint32_t*>(scr + kOffHeadReady);
   k.ar_done_bits = reinterpret_cast<unsigned long long*>(scr + kOffDoneBits);
-  k.ready_bits = reinterpret_cast<unsigned long long*>(scr + kOffReadyBits);
   k.ready_count = reinterpret_cast<uint32_t*>(scr + kOffReadyCount);
   k.oproj_queue = reinterpret_cast<uint32_t*>(scr + kOffQueue);
 

@@ -164,20 +164,9 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
 }
 
 // Shared-memory operand descriptor (sm_100 format): start address, leading / stride byte
-// offsets (all >> 4), version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= static_cast<uint64_t>(1) << 46;   // descriptor version (Blackwell)
-  d |= static_cast<uint64_t>(2) << 61;   // SWIZZLE_128B
-  return d;
-}
-
-// Same descriptor from parts: `tmpl` holds everything but the start address (see
-// smem_desc_template), `addr16` is the shared address >> 4.  Cheap enough to rebuild per MMA.
+// offsets (all >> 4), version 1, 128-byte swizzle.  Built from two parts: `tmpl` holds
+// everything but the start address, `addr16` is the shared address >> 4.  Cheap enough to
+// rebuild per MMA.
 __host__ __device__ constexpr uint64_t smem_desc_template(uint32_t lbo_bytes, uint32_t sbo_bytes) {
   return (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16) |
          (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) |
@@ -288,11 +277,6 @@ __device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ uint64_t ld_acquire_sys_u64(const uint64_t* p) {
-  uint64_t v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ uint32_t atom_add_relaxed_gpu(uint32_t* p, uint32_t v) {
   uint32_t o;
   asm volatile("atom.relaxed.gpu.global.add.u32 %0, [%1], %2;" : "=r"(o) : "l"(p), "r"(v)
@@ -308,12 +292,6 @@ __device__ __forceinline__ uint32_t atom_add_release_gpu(uint32_t* p, uint32_t v
 __device__ __forceinline__ uint32_t atom_add_acqrel_gpu(uint32_t* p, uint32_t v) {
   uint32_t o;
   asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(o) : "l"(p), "r"(v)
-               : "memory");
-  return o;
-}
-__device__ __forceinline__ uint32_t atom_add_acqrel_sys(uint32_t* p, uint32_t v) {
-  uint32_t o;
-  asm volatile("atom.acq_rel.sys.global.add.u32 %0, [%1], %2;" : "=r"(o) : "l"(p), "r"(v)
                : "memory");
   return o;
 }
@@ -338,33 +316,9 @@ __device__ __forceinline__ uint32_t atom_cas_acqrel_sys(uint32_t* p, uint32_t cm
                : "l"(p), "r"(cmp), "r"(v) : "memory");
   return o;
 }
-__device__ __forceinline__ uint32_t atom_cas_relaxed_gpu(uint32_t* p, uint32_t cmp, uint32_t v) {
-  uint32_t o;
-  asm volatile("atom.relaxed.gpu.global.cas.b32 %0, [%1], %2, %3;" : "=r"(o)
-               : "l"(p), "r"(cmp), "r"(v) : "memory");
-  return o;
-}
-__device__ __forceinline__ uint32_t atom_exch_relaxed_gpu(uint32_t* p, uint32_t v) {
-  uint32_t o;
-  asm volatile("atom.relaxed.gpu.global.exch.b32 %0, [%1], %2;" : "=r"(o) : "l"(p), "r"(v)
-               : "memory");
-  return o;
-}
-__device__ __forceinline__ uint64_t atom_and_acqrel_sys_u64(uint64_t* p, uint64_t v) {
-  uint64_t o;
-  asm volatile("atom.acq_rel.sys.global.and.b64 %0, [%1], %2;" : "=l"(o) : "l"(p), "l"(v)
-               : "memory");
-  return o;
-}
 __device__ __forceinline__ uint64_t atom_or_acqrel_gpu_u64(uint64_t* p, uint64_t v) {
   uint64_t o;
   asm volatile("atom.acq_rel.gpu.global.or.b64 %0, [%1], %2;" : "=l"(o) : "l"(p), "l"(v)
-               : "memory");
-  return o;
-}
-__device__ __forceinline__ uint64_t atom_or_release_sys_u64(uint64_t* p, uint64_t v) {
-  uint64_t o;
-  asm volatile("atom.release.sys.global.or.b64 %0, [%1], %2;" : "=l"(o) : "l"(p), "l"(v)
                : "memory");
   return o;
 }

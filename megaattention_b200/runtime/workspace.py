@@ -29,7 +29,7 @@ from ..metadata.row_desc import active_counts, oproj_task_counts
 
 NUM_CTRL = 8
 NUM_SYNC = 3
-NUM_STATUS = 8 + 11 * 2048 + 148 * 8 + 148 * 128     # 8 status words + room for the optional event trace
+NUM_STATUS = 8
 
 
 def claim_order(meta) -> np.ndarray:
@@ -119,8 +119,20 @@ class FusedFaOprojArWorkspace:
             csym_mc_ptr = 0
             rc_ptrs, rb_ptrs, nvl_peer_ptrs, csym_peer_ptrs = [], [], [], []
 
+        # varlen metadata: one device buffer, so a layer's descriptors arrive in one copy;
+        # cu_q | cu_k | fa_b | fa_mb | fa_order | actv are views at fixed (capacity) offsets,
+        # each 16-byte aligned
+        def up4(n):
+            return (n + 3) // 4 * 4
+        sizes = (max_num_batch + 1, max_num_batch + 1, max_num_row_tiles, max_num_row_tiles,
+                 max_num_row_tiles, 8)
+        offs = [0]
+        for n in sizes:
+            offs.append(offs[-1] + up4(n))
+        meta_dev = zeros(offs[-1], torch.int32)
+        mviews = [meta_dev[offs[i]:offs[i] + sizes[i]] for i in range(6)]
         ws = cls(
-            dev=dev, dtype=dtype, tp_size=tp_size, rank=rank, group_name=group_name,
+            dev=dev, dtype=dtype, meta_dev=meta_dev, _meta_offs=offs, tp_size=tp_size, rank=rank, group_name=group_name,
             H_local=H_local, H_kv=H_kv, D=D, K_local=K_local, hidden=hidden,
             hidden_pad=hidden_pad, N_TILE=N_TILE, super_group_n_tiles=super_group_n_tiles,
             q_per_kv=q_per_kv, num_out=num_out, num_super_groups=nsg,
@@ -129,15 +141,11 @@ class FusedFaOprojArWorkspace:
             paged=bool(paged), page_size=page_size,
             max_num_pages=max_num_pages, max_num_pages_per_seq=max_num_pages_per_seq,
             ctrl=zeros(NUM_CTRL, torch.uint32), sync_ctrl=zeros(NUM_SYNC, torch.uint32),
-            actv=zeros(6, torch.int32), status=zeros(NUM_STATUS, torch.uint32),
+            actv=mviews[5][:6], status=zeros(NUM_STATUS, torch.uint32),
             head_ready=zeros(max_num_row_tiles, torch.uint32),
             oproj_queue=zeros(max_total, torch.uint32),
             ar_done_bits=zeros(max_owner_words, torch.int64),
-            cu_q=zeros(max_num_batch + 1, torch.int32),
-            cu_k=zeros(max_num_batch + 1, torch.int32),
-            fa_b=zeros(max_num_row_tiles, torch.int32),
-            fa_mb=zeros(max_num_row_tiles, torch.int32),
-            fa_order=zeros(max_num_row_tiles, torch.int32),
+            cu_q=mviews[0], cu_k=mviews[1], fa_b=mviews[2], fa_mb=mviews[3], fa_order=mviews[4],
             Q=zeros((tot_cap, H_local, D), dtype),
             K=(None if paged else zeros((max_tot_k, H_kv, D), dtype)),
             V=(None if paged else zeros((max_tot_k, H_kv, D), dtype)),
@@ -320,22 +328,29 @@ class FusedFaOprojArWorkspace:
             self._set_meta(meta)
 
     def _set_meta(self, meta):
-        R, nb = meta.num_row_tiles, meta.num_batch
-        # one small H2D copy: cu_q | cu_k | fa_b | fa_mb | fa_order | actv packed on the host
-        host = np.concatenate([
-            np.asarray(meta.cu_seqlens_q, dtype=np.int32),
-            np.asarray(meta.cu_seqlens_k, dtype=np.int32),
-            np.asarray(meta.batch_idx, dtype=np.int32),
-            np.asarray(meta.m_block, dtype=np.int32),
-            claim_order(meta),
-            active_counts(R, self.H_local, self.num_super_groups, self.tp_size, self.rank),
-        ])
-        stage = torch.from_numpy(host).to(self.dev, non_blocking=False)
-        o = 0
-        for dst, n in ((self.cu_q, nb + 1), (self.cu_k, nb + 1), (self.fa_b, R),
-                       (self.fa_mb, R), (self.fa_order, R), (self.actv, 6)):
-            dst[:n].copy_(stage[o:o + n])
-            o += n
+        R = meta.num_row_tiles
+        # ONE asynchronous H2D copy: the six arrays are packed at their capacity offsets into
+        # a pinned staging buffer (a ring of four, so the host never rewrites a buffer whose
+        # copy may still be in flight)
+        if getattr(self, "_meta_ring", None) is None:
+            self._meta_ring = [[torch.zeros(self._meta_offs[-1], dtype=torch.int32).pin_memory(), None]
+                               for _ in range(4)]
+            self._meta_i = 0
+        slot = self._meta_ring[self._meta_i % 4]
+        self._meta_i += 1
+        if slot[1] is not None:
+            slot[1].synchronize()
+        buf = slot[0].numpy()
+        o = self._meta_offs
+        for i, arr in enumerate((meta.cu_seqlens_q, meta.cu_seqlens_k, meta.batch_idx, meta.m_block,
+                                 claim_order(meta),
+                                 active_counts(R, self.H_local, self.num_super_groups,
+                                               self.tp_size, self.rank))):
+            arr = np.asarray(arr, dtype=np.int32)
+            buf[o[i]:o[i] + arr.size] = arr
+        self.meta_dev.copy_(slot[0], non_blocking=True)
+        slot[1] = torch.cuda.Event()
+        slot[1].record(torch.cuda.current_stream(self.dev))
         self._meta = meta
 
     def _stream(self):
@@ -364,6 +379,7 @@ class FusedFaOprojArWorkspace:
     def launch_ar_only(self, extra_flags=0):
         """AllReduce stage alone over every slot of ``csym`` (tp > 1).  Every rank's partial
         must be complete before any rank launches (e.g. after a host barrier)."""
+        assert self.tp_size > 1, "the AllReduce stage needs tp_size > 1"
         self.launch(flags=_cabi.MA_FLAG_AR_ONLY | extra_flags)
 
     def check_status(self):

@@ -166,7 +166,7 @@ def bf16_half_ulp(x):
     return torch.exp2(torch.floor(torch.log2(a)) - 8.0)
 
 
-def err_beyond_rounding(got, ref_fp32, extra_half_ulps=0.0, partials=None):
+def err_beyond_rounding(got, ref_fp32, extra_half_ulps=0.0, partials=None, extra_slack=None):
     """``max(|got - ref| - r) / max|ref|`` where ``r`` is the rounding a bf16 result
     necessarily carries: half a bf16 ulp of the reference value (plus
     ``extra_half_ulps`` more half-ulps when the reference was itself rounded to bf16, plus
@@ -181,5 +181,7 @@ def err_beyond_rounding(got, ref_fp32, extra_half_ulps=0.0, partials=None):
     slack = bf16_half_ulp(r) * (1.0 + extra_half_ulps)
     for part in (partials or ()):
         slack = slack + bf16_half_ulp(part)
+    if extra_slack is not None:          # the partials' half-ulps, already summed elsewhere
+        slack = slack + extra_slack.float()
     excess = ((g - r).abs() - slack).clamp_min(0.0)
     return float(excess.max() / r.abs().max().clamp_min(1e-30))

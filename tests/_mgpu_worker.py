@@ -5,7 +5,9 @@ host-side reset (the pattern of the reference's tests/fused/test_fused_productio
 79-123): full capacity -> one tile, long KV -> short KV, repeats; every layer is checked
 against the CPU oracle (sum over ranks of the per-rank partial, one bf16 cast) and for a
 clean exit; two over-capacity layers must raise AssertionError and leave the workspace
-usable (test_fused_production.py:129-146).
+usable (test_fused_production.py:129-146).  The sequence is repeated for every AllReduce
+variant the kernel has, and the run ends with the tensor-parallel benchmark workload at
+full size against the oracle.
 """
 import os
 import sys
@@ -40,19 +42,7 @@ def inputs(layer, rank, sq, sk):
             rnd((sum(sk), hkv, 128), s + 2), rnd((H * 128, HIDDEN), s + 3, (H * 128) ** -0.5))
 
 
-def main():
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    dev = torch.device(f"cuda:{int(os.environ['LOCAL_RANK'])}")
-    torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
-    import torch.distributed._symmetric_memory as symm_mem
-    group = dist.group.WORLD.group_name
-    symm_mem.enable_symm_mem_for_group(group)
-    torch.set_num_threads(4)
-    ws = FusedFaOprojArWorkspace.create(
-        group, MAX_RT, HIDDEN, H, 128, tp_size=world, rank=rank, super_group_n_tiles=SG,
-        q_per_kv=QPK, max_tot_k=1536, device=dev)
-    ws.compile(w_fa=2, w_oproj=1, w_ar=1, num_ctas=int(os.environ.get("MA_TEST_CTAS", "24")))
+def run_layers(ws, rank, world, dev, tag):
     worst = 0.0
     for li, (sq, sk) in enumerate(LAYERS):
         sk = sq if sk is None else sk
@@ -73,7 +63,7 @@ def main():
         ctrl = ws.ctrl.cpu().tolist()
         tol = 8e-3 if sk != sq else 2e-3
         ok = e_comp <= tol and ctrl == [0] * 8
-        print(f"[rank {rank}] layer {li} {sq}/{sk}: err_comp={e_comp:.3g} err_rel_bf16={e_raw:.3g} "
+        print(f"[rank {rank}] {tag} layer {li} {sq}/{sk}: err_comp={e_comp:.3g} err_rel_bf16={e_raw:.3g} "
               f"ctrl={ctrl} {'OK' if ok else 'FAIL'}", flush=True)
         assert ok
         worst = max(worst, e_comp)
@@ -82,6 +72,75 @@ def main():
         lo, hi = mine_sum.clone(), mine_sum.clone()
         dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         assert float(lo) == float(hi), "ranks disagree on the reduced output"
+    return worst
+
+
+def run_c3(group, rank, world, dev, flags, p2p):
+    """The tensor-parallel benchmark workload at full size (22600 tokens, 64 q / 8 kv heads
+    split over the ranks, hidden 4096) against the CPU oracle: every rank computes the fp32
+    chain of its own head slice on the CPU, the partials are summed in fp32 across the ranks
+    (the reference's allreduce_reference: fused.py:207-212) and the kernel's reduced output
+    is compared with that sum on every rank."""
+    from megaattention_b200.workloads import WORKLOADS, make_rank_inputs
+    from megaattention_b200.metadata import choose_launch_config
+    from oracle.chain_oracle import bf16_half_ulp
+    wl = WORKLOADS["c3"]
+    h, hkv = wl.heads_local(world)
+    Q, K, V, W = make_rank_inputs(wl, world, rank)
+    meta = build_row_desc(wl.seqlens_q, seqlens_k=wl.seqlens_k)
+    cfg = choose_launch_config(meta, wl.hidden, world)
+    ws = FusedFaOprojArWorkspace.create(
+        group, meta.num_row_tiles, wl.hidden, h, 128, tp_size=world, rank=rank,
+        super_group_n_tiles=cfg.sg, q_per_kv=h // hkv, max_num_batch=meta.num_batch,
+        max_tot_k=wl.tot_k, device=dev)
+    ws.compile(w_fa=cfg.w_fa, w_oproj=cfg.w_oproj, w_ar=cfg.w_ar)
+    ws.default_flags, ws.ar_p2p = flags, p2p
+    ws.set_layer(meta, Q.to(dev), K.to(dev), V.to(dev), W.to(dev))
+    for _ in range(2):                      # the second launch starts from the first one's exit state
+        ws.launch()
+        ws.check_status()
+    assert ws.ctrl.cpu().tolist() == [0] * 8
+    torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
+    yp = oproj_oracle(fa_oracle(Q, K, V, wl.seqlens_q, wl.seqlens_k), W)
+    acc = yp.to(dev)
+    slack = bf16_half_ulp(yp).to(dev)
+    dist.all_reduce(acc)
+    dist.all_reduce(slack)
+    got = ws.output(meta).float()
+    e_comp = err_beyond_rounding(got, acc, extra_slack=slack)
+    e_raw = err_rel(got, acc)
+    ok = e_comp <= 2e-3
+    print(f"[rank {rank}] c3 tp{world} flags={flags} p2p={p2p}: err_comp={e_comp:.3g} "
+          f"err_rel_fp32={e_raw:.3g} {'OK' if ok else 'FAIL'}", flush=True)
+    assert ok
+    return e_comp
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device(f"cuda:{int(os.environ['LOCAL_RANK'])}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    import torch.distributed._symmetric_memory as symm_mem
+    from megaattention_b200 import _cabi
+    group = dist.group.WORLD.group_name
+    symm_mem.enable_symm_mem_for_group(group)
+    torch.set_num_threads(4)
+    ws = FusedFaOprojArWorkspace.create(
+        group, MAX_RT, HIDDEN, H, 128, tp_size=world, rank=rank, super_group_n_tiles=SG,
+        q_per_kv=QPK, max_tot_k=1536, device=dev)
+    ws.compile(w_fa=2, w_oproj=1, w_ar=1, num_ctas=int(os.environ.get("MA_TEST_CTAS", "24")))
+    # Every AllReduce variant runs the whole layer sequence on the same workspace: reductions
+    # as tasks of their own or riding along with O_proj tasks, and with two ranks through
+    # multimem as well as through peer loads.
+    variants = [("ar-tasks", 0, True), ("ar-ride", _cabi.MA_FLAG_AR_RIDE, True),
+                ("ar-ride+drain", _cabi.MA_FLAG_AR_RIDE | _cabi.MA_FLAG_DRAIN_FIRST, True)]
+    if world == 2:
+        variants += [("multimem", 0, False), ("multimem+ride", _cabi.MA_FLAG_AR_RIDE, False)]
+    worst = 0.0
+    for tag, flags, p2p in variants:
+        ws.default_flags, ws.ar_p2p = flags, p2p
+        worst = max(worst, run_layers(ws, rank, world, dev, tag))
     # over-capacity layers: AssertionError before anything is touched, workspace stays usable
     for sq, sk in (([1537], None), ([256], [1537])):
         sk2 = sq if sk is None else sk
@@ -96,6 +155,10 @@ def main():
     ws.set_layer(meta, *[t.to(dev) for t in inputs(2, rank, sq, sq)])
     ws.launch(); ws.check_status()
     dist.barrier()
+    if os.environ.get("MA_TEST_C3", "1") == "1":
+        for flags in (0, _cabi.MA_FLAG_AR_RIDE | _cabi.MA_FLAG_DRAIN_FIRST):
+            worst = max(worst, run_c3(group, rank, world, dev, flags, True))
+        dist.barrier()
     print(f"[rank {rank}] ALL OK worst err_comp={worst:.3g}", flush=True)
     dist.destroy_process_group()
 
