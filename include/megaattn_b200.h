@@ -110,6 +110,12 @@ typedef struct ma_plan_desc {
   uint64_t peer_csym[MA_MAX_TP];   /* per-rank addresses of C_sym (symmetric); needed for
                                       MA_FLAG_AR_P2P, may be 0 otherwise.  No reference
                                       counterpart: the reference reduces through multimem only. */
+  uint64_t audit;   /* optional (0 = off): u32[max_row_tiles*H_local + max_total_oproj +
+                       max_owner_slots], zeroed by the caller.  The kernel adds 1 for every
+                       attention (row tile, head), every O_proj slot and every owned AllReduce
+                       slot it finished: after a launch all active entries must read 1
+                       (exactly-once check; the reference has none, its status notes ask for
+                       one: docs/status/STATUS.md:42-53). */
 } ma_plan_desc;
 
 /* Role weights etc.: the arguments of FusedFaOprojArWorkspace.compile()

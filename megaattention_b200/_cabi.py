@@ -59,7 +59,8 @@ class PlanDesc(C.Structure):
            ("page_table", C.c_uint64), ("cache_seqlens", C.c_uint64),
            ("max_pages_per_seq", C.c_int32), ("reserved0", C.c_int32),
            ("fa_order", C.c_uint64),
-           ("peer_csym", C.c_uint64 * MA_MAX_TP)]
+           ("peer_csym", C.c_uint64 * MA_MAX_TP),
+           ("audit", C.c_uint64)]
     )
 
 

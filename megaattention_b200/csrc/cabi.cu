@@ -230,6 +230,9 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   k.cache_seqlens = reinterpret_cast<const int*>(d->cache_seqlens);
   k.pps = d->max_pages_per_seq;
   k.status = reinterpret_cast<uint32_t*>(d->status);
+  k.audit = reinterpret_cast<uint32_t*>(d->audit);
+  k.audit_op_base = d->max_row_tiles * d->H_local;
+  k.audit_ar_base = k.audit_op_base + static_cast<int>(max_total);
   k.csym_mc = d->csym_multicast;
   for (int r = 0; r < MA_MAX_TP; ++r) {
     k.peer_rc[r] = d->peer_ready_count[r];

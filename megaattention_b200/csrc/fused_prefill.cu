@@ -565,10 +565,20 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       bool ld_pending[2] = {false, false}, ld_skip[2] = {false, false};
       int pending_ticket = -1;
       uint32_t poll_no = 0;
-      int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0}, occ_ride[2] = {-1, -1};
+      int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0}, occ_h[2] = {0, 0}, occ_ride[2] = {-1, -1};
       const bool ar_ride = p.tp > 1 && (p.flags & 128u) && !(p.flags & (1u | 8u | 16u | 32u));
       auto publish = [&](int kk) {
         if (s_abort) return;
+        if (p.audit) {      // exactly-once audit: one count per finished unit of work
+          if (occ_mode[kk] == MODE_FA) {
+            for (int i = 0; i < occ_b[kk]; ++i) atomicAdd(p.audit + occ_a[kk] * p.H + occ_h[kk] + i, 1u);
+          } else if (occ_mode[kk] == MODE_OPROJ) {
+            atomicAdd(p.audit + p.audit_op_base + occ_a[kk], 1u);
+            if (occ_ride[kk] >= 0) atomicAdd(p.audit + p.audit_ar_base + occ_ride[kk] / p.tp, 1u);
+          } else if (occ_mode[kk] == MODE_AR) {
+            atomicAdd(p.audit + p.audit_ar_base + occ_a[kk] / p.tp, 1u);
+          }
+        }
         if (occ_mode[kk] == MODE_FA) {
           fence_acq_rel_gpu();
           const uint32_t old = atom_add_acqrel_gpu(p.head_ready + occ_a[kk],
@@ -650,7 +660,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           d[TF_QROW0] = q0 + mb * 128; d[TF_VALID] = min(128, q_len - mb * 128);
           d[TF_KSTART] = k0; d[TF_KLEN] = k_len; d[TF_OFFSET] = offset; d[TF_NBLK] = nblk;
           d[TF_MB] = mb;
-          occ_a[k] = ft; occ_b[k] = nt;
+          occ_a[k] = ft; occ_b[k] = nt; occ_h[k] = head0;
         } else if (mode == MODE_OPROJ || mode == MODE_AR) {
           const int ft = arg / p.nsg, g = arg % p.nsg;
           const int base_out = g * p.sg;

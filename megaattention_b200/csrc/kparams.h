@@ -50,6 +50,9 @@ struct KParams {
   const int* cache_seqlens;       // paged KV: KV length per sequence
   int pps;                        // page-table row pitch
   uint32_t* status;
+  uint32_t* audit;                // optional execution counters (null: off): one per attention
+                                  // (row tile, head), per O_proj slot, per owned AllReduce slot
+  int audit_op_base, audit_ar_base;
 
   unsigned long long csym_mc;
   unsigned long long peer_rc[kMaxTp];

@@ -86,3 +86,10 @@ def launch_flags_b200(meta, hidden: int, tp_size: int, H_local: int, D: int = 12
     t_compute = flops / 1.2e15
     t_ar = tot_q * hidden * 2.0 / 0.38e12
     return 2 if t_ar > 0.8 * t_compute else 0
+
+
+def num_ctas_b200(meta, hidden: int, tp_size: int, H_local: int, num_sms: int = 148) -> int:
+    """CTA count for the sm_100a kernel (no reference counterpart; the reference hard-codes
+    132).  One persistent CTA per SM: the calibration sweep
+    (``metadata/sweep_launch_config.py``) found no shape on which leaving SMs idle won."""
+    return int(num_sms)

@@ -171,12 +171,14 @@ class FusedFaOprojArWorkspace:
 
     # ------------------------------------------------------------------ compile
     def compile(self, w_fa=4, w_oproj=1, w_ar=1, num_ctas=None, kv_stages=2,
-                K_CHUNK=64, oproj_stages=4, softmax_scale=None, wait_limit_ms=0):
+                K_CHUNK=64, oproj_stages=4, softmax_scale=None, wait_limit_ms=0, audit=False):
         """Fix the launch configuration and build the C-ABI plan.
 
         ``kv_stages``, ``K_CHUNK`` and ``oproj_stages`` are accepted for signature
         compatibility; the staging depths of the sm_100a kernel are fixed.
-        ``num_ctas=None`` means one CTA per SM.
+        ``num_ctas=None`` means one CTA per SM.  ``audit=True`` adds execution counters
+        (``self.audit``: one per attention (row tile, head), per O_proj slot, per owned
+        AllReduce slot; see ``audit_counts``) for exactly-once checks.
         """
         if self._plan is not None:
             _cabi.lib.ma_plan_destroy(self._plan)
@@ -206,6 +208,12 @@ class FusedFaOprojArWorkspace:
                         ("fa_mb", self.fa_mb), ("status", self.status),
                         ("fa_order", self.fa_order)):
             setattr(d, name, t.data_ptr())
+        self.audit = None
+        if audit:
+            owner_slots = (self.max_total_oproj + self.tp_size - 1) // self.tp_size
+            self.audit = torch.zeros(self.max_num_row_tiles * self.H_local + self.max_total_oproj
+                                     + owner_slots, dtype=torch.int32, device=self.dev)
+            d.audit = self.audit.data_ptr()
         d.csym_multicast = self.csym_mc_ptr
         for r in range(self.tp_size if self.tp_size > 1 else 0):
             d.peer_ready_count[r] = self.rc_ptrs[r]
@@ -381,6 +389,19 @@ class FusedFaOprojArWorkspace:
         must be complete before any rank launches (e.g. after a host barrier)."""
         assert self.tp_size > 1, "the AllReduce stage needs tp_size > 1"
         self.launch(flags=_cabi.MA_FLAG_AR_ONLY | extra_flags)
+
+    def audit_counts(self, meta=None):
+        """``(attention [R, H_local], o_proj [R * nsg], allreduce [owned])`` execution
+        counts since the last ``audit.zero_()`` (``compile(audit=True)``)."""
+        meta = meta or self._meta
+        R = meta.num_row_tiles
+        a = self.audit.cpu()
+        n_fa, n_op = self.max_num_row_tiles * self.H_local, self.max_total_oproj
+        total = R * self.num_super_groups
+        owned = max(total - self.rank, 0)
+        owned = (owned + self.tp_size - 1) // self.tp_size
+        return (a[:R * self.H_local].view(R, self.H_local), a[n_fa:n_fa + total],
+                a[n_fa + n_op:n_fa + n_op + owned])
 
     def check_status(self):
         """Synchronise the launch stream and raise if a device-side wait gave up."""

@@ -34,7 +34,8 @@ def test_struct_layouts_match_the_header():
     assert _cabi.PlanDesc.page_table.offset == 56 + 21 * 8 + 3 * 64
     assert _cabi.PlanDesc.fa_order.offset == 56 + 21 * 8 + 3 * 64 + 24
     assert _cabi.PlanDesc.peer_csym.offset == 56 + 21 * 8 + 3 * 64 + 32
-    assert C.sizeof(_cabi.PlanDesc) == 56 + 21 * 8 + 3 * 64 + 32 + 64
+    assert _cabi.PlanDesc.audit.offset == 56 + 21 * 8 + 3 * 64 + 32 + 64
+    assert C.sizeof(_cabi.PlanDesc) == 56 + 21 * 8 + 3 * 64 + 32 + 64 + 8
     assert _cabi.NoAllocArgs.seqlens_q.offset == 40
     assert C.sizeof(_cabi.NoAllocArgs) == 40 + 2 * 8 + 5 * 8 + 8
 

@@ -25,7 +25,7 @@ SENT = -7.0
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 
 
-def run_case(name, w=(4, 1, 1), num_ctas=None, launches=1):
+def run_case(name, w=(4, 1, 1), num_ctas=None, launches=1, audit=True):
     from megaattention_b200.metadata import build_row_desc
     from megaattention_b200.runtime import FusedFaOprojArWorkspace
     sq, H, hidden, qpk, sk, seed = CASES[name]
@@ -34,12 +34,19 @@ def run_case(name, w=(4, 1, 1), num_ctas=None, launches=1):
     ws = FusedFaOprojArWorkspace.create(
         None, max_num_row_tiles=meta.num_row_tiles, hidden=hidden, H_local=H, D=128,
         q_per_kv=qpk, max_tot_k=int(meta.cu_seqlens_k[-1]), device="cuda:0")
-    ws.compile(w_fa=w[0], w_oproj=w[1], w_ar=w[2], num_ctas=num_ctas)
+    ws.compile(w_fa=w[0], w_oproj=w[1], w_ar=w[2], num_ctas=num_ctas, audit=audit)
     for _ in range(launches):
         ws.csym.fill_(SENT)
         ws.set_layer(meta, Q.cuda(), K.cuda(), V.cuda(), W.cuda())
         ws.launch()
         ws.check_status()
+    if audit:
+        # every attention (row tile, head), O_proj slot and (identity) AllReduce slot was
+        # executed exactly once per launch, and nothing outside the active range was touched
+        fa, op, ar = ws.audit_counts(meta)
+        assert bool((fa == launches).all()) and bool((op == launches).all()), (fa, op)
+        assert bool((ar == 0).all())        # one rank: the O_proj finisher accounts the slot
+        assert int(ws.audit.sum()) == launches * (fa.numel() + op.numel())
     O, Yp, Yf = full_chain_oracle(Q, K, V, W, sq, sk)
     oscr_ref = o_scratch_oracle(O, sq)
     oscr = ws.Oscr.float().cpu()
