@@ -38,8 +38,10 @@ typedef enum ma_error {
 
 /* ma_launch_args.flags */
 #define MA_FLAG_FA_ONLY 1u    /* run the attention stage only (fills O_scratch)         */
-#define MA_FLAG_DRAIN_FIRST 2u /* every CTA probes AllReduce, then O_proj, then attention
-                                  (no reference counterpart; for NVLink-bound launches)  */
+#define MA_FLAG_DRAIN_FIRST 2u /* downstream work first: attention- and O_proj-role CTAs probe
+                                  O_proj, attention, AllReduce; AllReduce-role CTAs probe
+                                  AllReduce, O_proj, attention (no reference counterpart; for
+                                  NVLink-bound launches, so that AllReduce traffic starts early) */
 #define MA_FLAG_AR_ONLY 8u    /* AllReduce stage only: every owned slot of C_sym is reduced;
                                  all ranks' partials must already be in place             */
 #define MA_FLAG_NO_AR 16u     /* stop after O_proj: C_sym holds this rank's partial (measurement aid) */

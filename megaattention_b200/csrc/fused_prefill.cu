@@ -674,7 +674,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             // The compute warps of an O_proj task mostly wait for the tensor pipe: give
             // them a ready AllReduce slot of this rank to reduce meanwhile.
             int ar_arg;
-            if (try_claim_ar(p, local_owned, poll_no++, &ar_arg)) {
+            if (try_claim_ar(p, local_owned, 0u, &ar_arg)) {       // this CTA's stretch only: short
               const int aft = ar_arg / p.nsg, ag = ar_arg % p.nsg;
               d[TO_AR_SLOT] = ar_arg; d[TO_AR_FT] = aft; d[TO_AR_BASE] = ag * p.sg;
               d[TO_AR_VNT] = min(p.sg, p.num_out - ag * p.sg);

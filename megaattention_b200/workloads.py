@@ -1,8 +1,11 @@
 """The benchmark / parity workloads and their seeded synthetic inputs.
 
 The reference measures on synthetic random tensors (benchmarks/
-bench_fused_fa_oproj_ar.py:158-200 builds them inline); the five configurations here
-are the ones the build's baseline file names.  Inputs are drawn on the CPU with a
+bench_fused_fa_oproj_ar.py:158-200 builds them inline); c1-c5 are five configurations of
+that kind (a CPU-sized case, the per-rank shape of an 8-way split 64-head model, its
+tensor-parallel sweep, a large-hidden case and a chunked-prefill case), long16k / long32k
+are the single-sequence shapes on which the reference's own sweep falls below its unfused
+baseline (benchmarks/sweep_results.md:11-14).  Inputs are drawn on the CPU with a
 seeded ``torch.Generator`` in fp32 and cast to bf16, so that a CPU checker and the GPU
 see identical bits.
 
@@ -68,6 +71,10 @@ WORKLOADS = {
     # Chunked prefill, k = 4 q, per rank 8 q / 1 kv heads, 8 ranks.
     "c5": Workload("c5", _SMALL, 64, 8, 4096, [8], kv_mult=4, w_fan_in=1024,
                    per_rank_seed=True),
+    # One long sequence, 8 q / 1 kv heads, hidden 2048, one rank: the tail of the launch is
+    # one chain of ever longer attention tasks per head.
+    "long16k": Workload("long16k", [16384], 8, 1, 2048, [1]),
+    "long32k": Workload("long32k", [32768], 8, 1, 2048, [1]),
 }
 
 

@@ -191,10 +191,10 @@ def test_kernel_error_is_the_floor_of_its_staging(name):
     ``oracle/numerics_model.py`` computes what a pipeline with the kernel's rounding points
     (bf16 P per key block, bf16 O_scratch, bf16 output) gives when everything in between is
     exact fp32.  The kernel's raw err_rel against the fp32 chain must not exceed 1.25x the
-    model's, and kernel and model must agree to one bf16 ulp on all but a sliver of the
-    elements (both are bf16 roundings of nearly the same fp32 value), at every stage."""
+    model's, and kernel and model must give the very same bf16 value for most elements (both
+    round nearly the same fp32 value) and never differ by more than one ulp of the top
+    binade, for the attention output and for the final output."""
     from oracle.numerics_model import chain_model
-    from oracle.chain_oracle import bf16_half_ulp
     sq, H, hidden, qpk, sk, seed = CASES[name]
     Q, K, V, W = make_inputs(name)
     res = run_case(name)
@@ -205,14 +205,15 @@ def test_kernel_error_is_the_floor_of_its_staging(name):
     # O_scratch (valid rows) against the model's attention output
     tiles = tile_coords(sq)
     got_o = torch.cat([res["oscr"][t, :vm] for t, (s0, vm) in enumerate(tiles)])
-    for got, want, what in ((got_o, Om.float(), "O_scratch"), (res["out"].float(), Ym.float(), "output")):
-        ulp = 2.0 * bf16_half_ulp(want)
+    for got, want, what, min_equal in ((got_o, Om.float(), "O_scratch", 0.85),
+                                       (res["out"].float(), Ym.float(), "output", 0.5)):
         d = (got - want).abs()
-        frac_gt1 = float((d > 1.001 * ulp).float().mean())
-        worst = float((d / ulp).max())
-        print(f"  {what}: elements off by more than one ulp {frac_gt1:.2e}, worst {worst:.2f} ulp, "
-              f"equal {float((d == 0).float().mean()):.3f}")
-        assert frac_gt1 < 2e-3 and worst <= 4.0, (what, frac_gt1, worst)
+        equal = float((d == 0).float().mean())
+        worst = float(d.max() / want.abs().max())
+        print(f"  {what}: bit-equal to the model {equal:.3f}, worst difference {worst:.2e} of the maximum")
+        # most elements are the same bf16 value; none is further off than one ulp of the top
+        # binade (2^-7 of the maximum)
+        assert equal >= min_equal and worst <= 2.0 ** -7, (what, equal, worst)
 
 
 def test_stage_flags_that_do_not_fit_the_plan_are_refused():
