@@ -189,6 +189,54 @@ __device__ __forceinline__ bool try_claim_ar(const KParams& p, int local_owned, 
   return false;
 }
 
+// The same claim, guided by the O_proj ready queue instead of a stretch of the count array.
+// Row tiles finish their attention in roughly the same order on every rank, so the slots
+// that have collected all tp arrivals are, nearly always, those of the oldest entries of
+// this rank's own ready queue that have not been reduced yet.  ctrl[C_AR_CURSOR] counts the
+// row-tile entries of the queue (nsg consecutive slots each) whose owned slots are all
+// claimed; a claim looks at the owned slots of the next few entries (up to 16 counts, read
+// in two batches) and takes the first that is ready.  This is what lets a CTA that is busy
+// with other work pick up a slot at the moment it takes an O_proj task.
+__device__ __noinline__ int try_claim_ar_queue(const KParams& p) {
+  const uint32_t nsg = static_cast<uint32_t>(p.nsg), tp = static_cast<uint32_t>(p.tp);
+  const uint32_t cur = ld_relaxed_gpu(p.ctrl + C_AR_CURSOR);
+  const uint32_t tail = ld_acquire_gpu(p.ctrl + C_OP_PUBLISH) / nsg;
+  const uint32_t opr = (nsg + tp - 1) / tp;            // owned slots per entry, at most
+  if (cur >= tail || opr > 16u) return -1;             // (more than 16: the other path)
+  const uint32_t n_use = min(min(8u, tail - cur), 16u / opr);
+  // candidate c = owned slot number c % opr of entry c / opr; everything below is indexed by
+  // unrolled constants so that it stays in registers
+  uint32_t cand[16], cnt[16];
+#pragma unroll
+  for (uint32_t c = 0; c < 16; ++c) {
+    const uint32_t u = c / opr, k = c - u * opr;
+    cand[c] = 0xFFFFFFFFu;
+    if (u < n_use) {
+      const uint32_t base = (ld_relaxed_gpu(p.oproj_queue + (cur + u) * nsg) / nsg) * nsg;
+      const uint32_t g = (tp + static_cast<uint32_t>(p.rank) - base % tp) % tp + k * tp;
+      if (g < nsg) cand[c] = base + g;
+    }
+  }
+#pragma unroll
+  for (uint32_t c = 0; c < 16; ++c)     // slots that do not exist count as claimed
+    cnt[c] = (cand[c] != 0xFFFFFFFFu) ? ld_relaxed_sys(p.ready_count + cand[c] / tp) : kArClaimed;
+  int found = -1;
+  uint32_t first_open = 16;             // first candidate that still waits for arrivals
+#pragma unroll
+  for (uint32_t c = 0; c < 16; ++c) {
+    if (found < 0 && cnt[c] == tp) {
+      const uint32_t old = atom_cas_acqrel_sys(p.ready_count + cand[c] / tp, tp, tp | kArClaimed);
+      cnt[c] = tp | kArClaimed;         // taken by this CTA or, a moment ago, by another one
+      if (old == tp) found = static_cast<int>(cand[c]);
+    }
+    if (!(cnt[c] & kArClaimed) && first_open == 16u) first_open = c;
+  }
+  // move the cursor past the leading entries whose owned slots are all claimed
+  const uint32_t adv = min(first_open / opr, n_use);
+  if (adv) atomicCAS(p.ctrl + C_AR_CURSOR, cur, cur + adv);
+  return found;
+}
+
 __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, int total_op,
                                            int local_owned, uint32_t poll_no, int* pending,
                                            int* mode, int* arg) {
@@ -245,7 +293,12 @@ __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, i
     if (m == MODE_FA) ok = try_fa(p, num_fa, arg);
     else if (fa_only) ok = false;
     else if (m == MODE_OPROJ) ok = try_pop_oproj(p, total_op, pending, arg);
-    else if (p.tp > 1 && !(p.flags & 16u)) ok = try_claim_ar(p, local_owned, poll_no, arg);
+    else if (p.tp > 1 && !(p.flags & 16u))
+    {
+      const int q = try_claim_ar_queue(p);
+      if (q >= 0) { *arg = q; ok = true; }
+      else ok = try_claim_ar(p, local_owned, poll_no, arg);
+    }
     if (ok) { *mode = m; return; }
   }
 }
@@ -673,8 +726,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           if (mode == MODE_OPROJ && ar_ride) {
             // The compute warps of an O_proj task mostly wait for the tensor pipe: give
             // them a ready AllReduce slot of this rank to reduce meanwhile.
-            int ar_arg;
-            if (try_claim_ar(p, local_owned, 0u, &ar_arg)) {       // this CTA's stretch only: short
+            const int ar_arg = try_claim_ar_queue(p);
+            if (ar_arg >= 0) {
               const int aft = ar_arg / p.nsg, ag = ar_arg % p.nsg;
               d[TO_AR_SLOT] = ar_arg; d[TO_AR_FT] = aft; d[TO_AR_BASE] = ag * p.sg;
               d[TO_AR_VNT] = min(p.sg, p.num_out - ag * p.sg);
@@ -1051,17 +1104,22 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT], valid_m = d[TO_VALID];
         const bool leader = ((warp & 3) == 0 && lane == 0);
         const uint32_t stg = smem0 + kSmOpStaging + wg * kPanel;   // [128 rows][64 cols] bf16
-        // An AllReduce slot riding along: one batch of reductions goes out before each wait
-        // for an accumulator and is stored after that pass's epilogue, so the NVLink round
-        // trips pass while the tensor pipe works; what is left is done after the last pass.
+        // An AllReduce slot riding along: per pass one batch of reductions goes out before
+        // the wait for the accumulator and is stored right after it, and another goes out
+        // before the epilogue and is stored after it, so the NVLink round trips pass while
+        // the tensor pipe works or the epilogue runs; what is left is done after the last
+        // pass.
         ArCursor arc{d[TO_AR_FT], d[TO_AR_BASE], tid - 128, 0};
         if (d[TO_AR_SLOT] >= 0) arc.total = d[TO_AR_VNT] * 2048;
         uint4 arv[16];
         for (int h = 0; h * 2 < vnt; ++h) {
-          const int ar_n = ar_batch_n(p, arc);
-          if (ar_n) ar_load(p, arc, ar_n, arv);
+          const int ar_n0 = ar_batch_n(p, arc);
+          if (ar_n0) ar_load(p, arc, ar_n0, arv);
           wait_bar(env, smem_u32(&bars.acc_full[h]), acc_par[h], 0xB0 + h);
           acc_par[h] ^= 1u;
+          if (ar_n0) ar_store(p, arc, ar_n0, arv);
+          const int ar_n = ar_batch_n(p, arc);
+          if (ar_n) ar_load(p, arc, ar_n, arv);
           tc_fence_after();
           const int o_t = 2 * h + wg;                   // column tile inside the super-group
           if (o_t < vnt) {

@@ -32,17 +32,26 @@ NUM_SYNC = 3
 NUM_STATUS = 8
 
 
-def claim_order(meta) -> np.ndarray:
+def claim_order(meta, prime: int = 0) -> np.ndarray:
     """Row tiles sorted by the number of 128-key blocks their attention task visits,
     longest first (stable), so the biggest tasks are claimed first and the tail of the
-    launch is filled with small ones.  Same on every rank."""
+    launch is filled with small ones.  Same on every rank.
+
+    ``prime`` > 0 moves that many of the shortest row tiles to the front: their attention
+    finishes within microseconds, so O_proj and AllReduce work exists almost from the start
+    of the launch instead of only after the first long attention task (tens of
+    microseconds) — worth it when the launch is bound by the AllReduce."""
     M = meta.M_TILE
     b = meta.batch_idx.astype(np.int64)
     lq = np.diff(meta.cu_seqlens_q.astype(np.int64))[b]
     lk = np.diff(meta.cu_seqlens_k.astype(np.int64))[b]
     last_row = (meta.m_block.astype(np.int64) + 1) * M + (lk - lq)
     nblk = np.minimum(-(-lk // M), -(-last_row // M))
-    return np.argsort(-nblk, kind="stable").astype(np.int32)
+    order = np.argsort(-nblk, kind="stable").astype(np.int32)
+    prime = int(min(max(prime, 0), order.size))
+    if prime:
+        order = np.concatenate([order[order.size - prime:][::-1], order[:order.size - prime]])
+    return order
 
 
 class FusedFaOprojArWorkspace:
@@ -53,6 +62,7 @@ class FusedFaOprojArWorkspace:
         self._meta = None
         self.default_flags = 0   # OR of _cabi.MA_FLAG_* applied by launch()
         self.ar_p2p = True       # tp_size == 2: AllReduce through peer loads instead of multimem
+        self.fa_prime_tiles = 0  # see claim_order
 
     # ------------------------------------------------------------------ create
     @classmethod
@@ -351,7 +361,7 @@ class FusedFaOprojArWorkspace:
         buf = slot[0].numpy()
         o = self._meta_offs
         for i, arr in enumerate((meta.cu_seqlens_q, meta.cu_seqlens_k, meta.batch_idx, meta.m_block,
-                                 claim_order(meta),
+                                 claim_order(meta, self.fa_prime_tiles),
                                  active_counts(R, self.H_local, self.num_super_groups,
                                                self.tp_size, self.rank))):
             arr = np.asarray(arr, dtype=np.int32)
