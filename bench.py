@@ -306,15 +306,26 @@ def main():
         if world > 1:
             dist.barrier()
 
+    gate = torch.zeros(1, device=dev)
+
+    def align():
+        """Start the ranks' next launch together: a short device-side sleep absorbs the host's
+        enqueue jitter, then a tiny all-reduce, which ends on all ranks at the same moment, is
+        the last thing on the stream before the timed launch.  Without it a rank whose host
+        was late starts late, and the other ranks' launches (which wait for its partial sums)
+        are charged for the delay."""
+        if world > 1:
+            torch.cuda._sleep(1000000)
+            dist.all_reduce(gate)
+
     def timed(fn, steps, warmup):
         for _ in range(warmup):
-            flush.zero_(); fn()
+            flush.zero_(); align(); fn()
         torch.cuda.synchronize(); barrier()
         evs = []
         for _ in range(steps):
             flush.zero_()
-            if world > 1:
-                torch.cuda._sleep(200000)      # let slower ranks' queues catch up
+            align()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream); fn(); b.record(stream)
             evs.append((a, b))

@@ -51,10 +51,12 @@ typedef enum ma_error {
                                   multicast path runs far below the NVLink copy rate).  Same sum:
                                   fp32, rounded once.  No reference counterpart. */
 #define MA_FLAG_TILE_ORDER 4u /* claim attention tasks in row-tile order, ignoring fa_order */
-#define MA_FLAG_AR_RIDE 128u  /* tp_size > 1: a ready AllReduce slot of this rank rides along with
-                                 each O_proj task; its reductions are in flight while the compute
-                                 warps wait for the tensor pipe.  Results are bit-identical with
-                                 and without it.  No reference counterpart. */
+#define MA_FLAG_AR_DEDICATED 256u /* tp_size > 1: CTAs of the AllReduce role (w_ar of every
+                                 w_fa + w_oproj + w_ar) take only AllReduce slots until every
+                                 slot this rank owns is reduced; the other CTAs reduce only when
+                                 they find no attention or O_proj task.  The reference's roles
+                                 are a bias, never a partition; this makes the AllReduce role
+                                 one.  No reference counterpart. */
 /* ma_launch refuses (MA_ERR_INVALID): more than one of FA_ONLY / AR_ONLY / NO_AR / OPROJ_ONLY;
  * AR_ONLY on one rank or without a multicast address; OPROJ_ONLY with tp_size > 1; AR_P2P unless
  * tp_size == 2 with both peer_csym set; unknown bits. */

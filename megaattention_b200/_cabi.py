@@ -18,7 +18,7 @@ MA_FLAG_AR_ONLY = 8
 MA_FLAG_NO_AR = 16
 MA_FLAG_OPROJ_ONLY = 32
 MA_FLAG_AR_P2P = 64
-MA_FLAG_AR_RIDE = 128
+MA_FLAG_AR_DEDICATED = 256
 
 MA_OK = 0
 MA_ERR_INVALID = -1

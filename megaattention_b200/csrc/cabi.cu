@@ -269,7 +269,7 @@ int ma_launch(ma_plan* pl, const ma_launch_args* a, void* stream) {
       (kp.tp != 2 || !pl->desc.peer_csym[0] || !pl->desc.peer_csym[1]))
     return MA_ERR_INVALID;
   if (kp.flags & ~(MA_FLAG_FA_ONLY | MA_FLAG_DRAIN_FIRST | MA_FLAG_TILE_ORDER | MA_FLAG_AR_ONLY |
-                   MA_FLAG_NO_AR | MA_FLAG_OPROJ_ONLY | MA_FLAG_AR_P2P | MA_FLAG_AR_RIDE))
+                   MA_FLAG_NO_AR | MA_FLAG_OPROJ_ONLY | MA_FLAG_AR_P2P | MA_FLAG_AR_DEDICATED))
     return MA_ERR_INVALID;
   if (kp.w_fa < 0 || kp.w_oproj < 0 || kp.w_ar < 0 || kp.w_fa + kp.w_oproj + kp.w_ar < 1)
     return MA_ERR_INVALID;

@@ -13,9 +13,7 @@
 //                                       streams once per pass)
 //   AR task    (owned slot)           : multimem.ld_reduce / multimem.st over the NVLS
 //                                       multicast view of the symmetric output (or plain
-//                                       peer loads / stores with two ranks); an owned slot
-//                                       can also ride along with an O_proj task, its
-//                                       reductions in flight while the tensor pipe works
+//                                       peer loads / stores with two ranks)
 //
 // Warp roles (12 warps, 384 threads):
 //   warp 0 (lane 0)  TMA producer: Q tiles, the K/V ring, O_proj stages
@@ -152,89 +150,68 @@ __device__ __forceinline__ bool try_pop_oproj(const KParams& p, int total_op, in
 // set bit (fused_fa_oproj_ar.py:192-239, 294-317).  On NVSwitch that costs every O_proj
 // task a blocking remote round trip (tens of microseconds once the links carry the
 // AllReduce itself) and makes all polling CTAs fight for one bit.  Here arrivals are
-// fire-and-forget adds on the owner's ready_count; a slot is ready when its count equals
-// tp, and the owner's CTAs each watch their own stretch of the count array (plus a few
-// neighbours', and now and then all of it), claiming with a compare-and-swap that marks the
-// count.  The reference's ready bitset has no role here (the plan descriptor still has
-// the field so that the workspace keeps the reference's buffer list; it may be 0).
-constexpr uint32_t kArClaimed = 0x40000000u;
-__device__ __forceinline__ bool try_claim_ar(const KParams& p, int local_owned, uint32_t poll_no,
-                                             int* arg) {
-  const int n = local_owned;
-  if (n <= 0) return false;
-  const int per = (n + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-  const int base = static_cast<int>((static_cast<long long>(blockIdx.x) * per) % n);
-  int span = ((poll_no & 7u) == 7u) ? n : per * 4 + 8;
-  if (span > n) span = n;
-  const uint32_t want = static_cast<uint32_t>(p.tp);
-  for (int j0 = 0; j0 < span; j0 += 8) {
-    uint32_t c[8];
+// fire-and-forget adds on the owner's ready counts and the owner finds ready slots by
+// reading the counts: they are packed as one byte per slot (tp <= 8 arrivals; bit 7 marks
+// a slot as claimed), so sixteen slots come with one 16-byte load and a scan of all the
+// slots a rank owns is a handful of loads - cheap enough that every CTA looks at every
+// slot each time it asks for work, and no ready slot waits to be discovered.  A CTA starts
+// its scan at a place of its own so that CTAs polling at the same moment do not all go for
+// the same slot; the claim is an atomic OR of the slot's flag, won by whoever sees the
+// flag clear in the value that comes back.  The reference's ready bitset has no role here
+// (the plan descriptor still has the field so that the workspace keeps the reference's
+// buffer list; it may be 0).
+__device__ __noinline__ int try_claim_ar(const KParams& p, int local_owned, uint32_t poll_no) {
+  if (local_owned <= 0) return -1;
+  const uint32_t tp = static_cast<uint32_t>(p.tp);
+  const uint32_t n_words = (static_cast<uint32_t>(local_owned) + 3u) >> 2;   // 4 slots per word
+  const uint32_t n_vec = (n_words + 3u) >> 2;                                // 16 slots per load
+  const uint32_t cap_words = static_cast<uint32_t>(p.max_owner_slots);       // buffer length
+  const uint32_t start = (blockIdx.x * 5u + poll_no) % n_vec;
+  for (uint32_t v0 = 0; v0 < n_vec; v0 += 8) {
+    uint4 w[8];
+    uint32_t vi[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      int idx = base + j0 + u;
-      if (idx >= n) idx -= n;
-      c[u] = (j0 + u < span) ? ld_relaxed_sys(p.ready_count + idx) : 0u;
+    for (uint32_t u = 0; u < 8; ++u) {
+      uint32_t v = start + v0 + u;
+      if (v >= n_vec) v -= n_vec;
+      vi[u] = v;
+      w[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (v0 + u < n_vec) {
+        // (gpu-scope loads: a hint only - the atomic below is the synchronising access)
+        const uint32_t* src = p.ready_count + v * 4;
+        if (v * 4 + 4 <= cap_words) {
+          w[u] = ld_relaxed_gpu_b128(src);
+        } else {                     // last, partial vector of a short buffer
+          if (v * 4 + 0 < cap_words) w[u].x = ld_relaxed_gpu(src + 0);
+          if (v * 4 + 1 < cap_words) w[u].y = ld_relaxed_gpu(src + 1);
+          if (v * 4 + 2 < cap_words) w[u].z = ld_relaxed_gpu(src + 2);
+        }
+      }
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      if (c[u] != want) continue;
-      int idx = base + j0 + u;
-      if (idx >= n) idx -= n;
-      if (atom_cas_acqrel_sys(p.ready_count + idx, want, want | kArClaimed) == want) {
-        *arg = idx * p.tp + p.rank;
-        return true;
+    for (uint32_t u = 0; u < 8; ++u) {
+      const uint32_t ws[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+#pragma unroll
+      for (uint32_t k = 0; k < 4; ++k) {
+        // bytes equal to tp (a claimed slot reads tp | 0x80, an unfinished one < tp)
+        const uint32_t x = ws[k] ^ (tp * 0x01010101u);
+        uint32_t hit = (x - 0x01010101u) & ~x & 0x80808080u;
+        while (hit) {
+          const uint32_t b = (__ffs(hit) - 1) >> 3;            // byte number 0..3
+          hit &= ~(0xFFu << (b * 8));
+          if (((ws[k] >> (b * 8)) & 0xFFu) != tp) continue;      // borrow artefact
+          const uint32_t idx = (vi[u] * 4 + k) * 4 + b;
+          if (idx >= static_cast<uint32_t>(local_owned)) continue;
+          const uint32_t old = atom_or_relaxed_sys(p.ready_count + vi[u] * 4 + k, 0x80u << (b * 8));
+          if (((old >> (b * 8)) & 0xFFu) == tp) {
+            fence_acq_rel_sys();      // the tp arrivals (release) happen before what follows
+            return static_cast<int>(idx * tp + p.rank);
+          }
+        }
       }
     }
   }
-  return false;
-}
-
-// The same claim, guided by the O_proj ready queue instead of a stretch of the count array.
-// Row tiles finish their attention in roughly the same order on every rank, so the slots
-// that have collected all tp arrivals are, nearly always, those of the oldest entries of
-// this rank's own ready queue that have not been reduced yet.  ctrl[C_AR_CURSOR] counts the
-// row-tile entries of the queue (nsg consecutive slots each) whose owned slots are all
-// claimed; a claim looks at the owned slots of the next few entries (up to 16 counts, read
-// in two batches) and takes the first that is ready.  This is what lets a CTA that is busy
-// with other work pick up a slot at the moment it takes an O_proj task.
-__device__ __noinline__ int try_claim_ar_queue(const KParams& p) {
-  const uint32_t nsg = static_cast<uint32_t>(p.nsg), tp = static_cast<uint32_t>(p.tp);
-  const uint32_t cur = ld_relaxed_gpu(p.ctrl + C_AR_CURSOR);
-  const uint32_t tail = ld_acquire_gpu(p.ctrl + C_OP_PUBLISH) / nsg;
-  const uint32_t opr = (nsg + tp - 1) / tp;            // owned slots per entry, at most
-  if (cur >= tail || opr > 16u) return -1;             // (more than 16: the other path)
-  const uint32_t n_use = min(min(8u, tail - cur), 16u / opr);
-  // candidate c = owned slot number c % opr of entry c / opr; everything below is indexed by
-  // unrolled constants so that it stays in registers
-  uint32_t cand[16], cnt[16];
-#pragma unroll
-  for (uint32_t c = 0; c < 16; ++c) {
-    const uint32_t u = c / opr, k = c - u * opr;
-    cand[c] = 0xFFFFFFFFu;
-    if (u < n_use) {
-      const uint32_t base = (ld_relaxed_gpu(p.oproj_queue + (cur + u) * nsg) / nsg) * nsg;
-      const uint32_t g = (tp + static_cast<uint32_t>(p.rank) - base % tp) % tp + k * tp;
-      if (g < nsg) cand[c] = base + g;
-    }
-  }
-#pragma unroll
-  for (uint32_t c = 0; c < 16; ++c)     // slots that do not exist count as claimed
-    cnt[c] = (cand[c] != 0xFFFFFFFFu) ? ld_relaxed_sys(p.ready_count + cand[c] / tp) : kArClaimed;
-  int found = -1;
-  uint32_t first_open = 16;             // first candidate that still waits for arrivals
-#pragma unroll
-  for (uint32_t c = 0; c < 16; ++c) {
-    if (found < 0 && cnt[c] == tp) {
-      const uint32_t old = atom_cas_acqrel_sys(p.ready_count + cand[c] / tp, tp, tp | kArClaimed);
-      cnt[c] = tp | kArClaimed;         // taken by this CTA or, a moment ago, by another one
-      if (old == tp) found = static_cast<int>(cand[c]);
-    }
-    if (!(cnt[c] & kArClaimed) && first_open == 16u) first_open = c;
-  }
-  // move the cursor past the leading entries whose owned slots are all claimed
-  const uint32_t adv = min(first_open / opr, n_use);
-  if (adv) atomicCAS(p.ctrl + C_AR_CURSOR, cur, cur + adv);
-  return found;
+  return -1;
 }
 
 __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, int total_op,
@@ -281,7 +258,13 @@ __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, i
   // three orders).  With the "drain first" launch flag downstream work goes first so that
   // AllReduce traffic starts early and keeps flowing: roles 0/1 become 3: OPROJ,FA,AR and
   // role 2 becomes 4: AR,OPROJ,FA.
-  for (int i = 0; i < 3; ++i) {
+  // With the "dedicated" launch flag the AllReduce-role CTAs take nothing but AllReduce
+  // slots until every slot this rank owns is reduced: NVLink round trips and the fences
+  // that wait for them then stay on those SMs and off the ones doing tensor work.
+  const bool ar_only_cta = (p.flags & 256u) && p.tp > 1 && (role == 2 || role == 4) &&
+                           !(p.flags & 16u) &&
+                           static_cast<int>(ld_relaxed_gpu(p.ctrl + C_AR_DONE)) < local_owned;
+  for (int i = 0; i < (ar_only_cta ? 1 : 3); ++i) {
     int m;
     if (role == 3) m = (i == 0) ? MODE_OPROJ : (i == 1) ? MODE_FA : MODE_AR;
     else if (role == 4) m = MODE_AR - i;
@@ -295,9 +278,8 @@ __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, i
     else if (m == MODE_OPROJ) ok = try_pop_oproj(p, total_op, pending, arg);
     else if (p.tp > 1 && !(p.flags & 16u))
     {
-      const int q = try_claim_ar_queue(p);
+      const int q = try_claim_ar(p, local_owned, poll_no);
       if (q >= 0) { *arg = q; ok = true; }
-      else ok = try_claim_ar(p, local_owned, poll_no, arg);
     }
     if (ok) { *mode = m; return; }
   }
@@ -341,10 +323,10 @@ __device__ __noinline__ void publish_ar_ready(const KParams& p, int slot) {
     fence_acq_rel_gpu();
     finish_ar_slot(p, slot);
   } else {
-    fence_acq_rel_sys();
     const int owner_rank = slot % p.tp;
     const int owner_idx = slot / p.tp;
-    red_add_release_sys(reinterpret_cast<uint32_t*>(p.peer_rc[owner_rank]) + owner_idx, 1u);
+    red_add_release_sys(reinterpret_cast<uint32_t*>(p.peer_rc[owner_rank]) + (owner_idx >> 2),
+                        1u << ((owner_idx & 3) * 8));      // one byte per slot
   }
   atom_add_release_gpu(p.ctrl + C_OP_DONE, 1u);
 }
@@ -426,10 +408,9 @@ __device__ __forceinline__ void stage_row32(uint32_t panel, int row, int col0,
 
 // ---------------------------------------------------------------- AllReduce of one slot
 // A slot is 128 rows x (vnt x 128) bf16 columns = vnt x 2048 chunks of 16 bytes.  The 256
-// compute threads walk it in batches; a batch is split into its loads (ar_load: up to 16
-// 16-byte requests per thread go out, nothing waits) and its stores (ar_store: the first
-// use of the loaded registers, i.e. where the thread waits for the round trip), so the
-// caller can put other work between the two.
+// compute threads walk it in batches; in a batch every thread first issues all its loads
+// (up to 16 requests of 16 bytes, nothing waits in between: NVLink round trips are
+// microseconds) and then stores the results.
 //   multimem path: 16 (or, for the last odd column tile, 8) multimem.ld_reduce per thread
 //     (fp32 sum of all ranks' bf16 taken in the switch), then multimem.st to every rank;
 //   peer path (MA_FLAG_AR_P2P, two ranks): 8 chunks per thread, the peer's and this rank's
@@ -456,7 +437,7 @@ __device__ __forceinline__ void ar_load(const KParams& p, const ArCursor& a, int
       v[u] = ld_relaxed_sys_b128(peer + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2);
 #pragma unroll
     for (int u = 0; u < 8; ++u)
-      v[8 + u] = ld_relaxed_sys_b128(mine + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2);
+      v[8 + u] = ld_relaxed_gpu_b128(reinterpret_cast<const void*>(mine + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2));   // this GPU's own partial
   } else if (n == 16) {
 #pragma unroll
     for (int u = 0; u < 16; ++u)
@@ -490,7 +471,7 @@ __device__ __forceinline__ void ar_store(const KParams& p, ArCursor& a, int n, c
   }
   a.c0 += kArThreads * n;
 }
-// Whatever is left of a slot, batch after batch.
+// A whole slot, batch after batch.
 __device__ __forceinline__ void ar_rest(const KParams& p, ArCursor& a) {
   uint4 v[16];
   for (int n = ar_batch_n(p, a); n > 0; n = ar_batch_n(p, a)) {
@@ -505,9 +486,7 @@ __device__ __forceinline__ void ar_rest(const KParams& p, ArCursor& a) {
 enum : int { T_MODE = 0, T_FT = 1,
              TF_HEAD0 = 2, TF_NT = 3, TF_KVH = 4, TF_QROW0 = 5, TF_VALID = 6, TF_KSTART = 7,
              TF_KLEN = 8, TF_OFFSET = 9, TF_NBLK = 10, TF_MB = 11,
-             TO_BASE = 2, TO_VNT = 3, TO_VALID = 4, TO_SLOT = 5,
-             // an owned AllReduce slot riding along with an O_proj task (TO_AR_SLOT < 0: none)
-             TO_AR_SLOT = 6, TO_AR_FT = 7, TO_AR_BASE = 8, TO_AR_VNT = 9, T_WORDS = 12 };
+             TO_BASE = 2, TO_VNT = 3, TO_VALID = 4, TO_SLOT = 5, T_WORDS = 12 };
 
 __device__ __forceinline__ bool is_tile_mode(int m) { return m == MODE_FA || m == MODE_OPROJ; }
 
@@ -618,8 +597,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       bool ld_pending[2] = {false, false}, ld_skip[2] = {false, false};
       int pending_ticket = -1;
       uint32_t poll_no = 0;
-      int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0}, occ_h[2] = {0, 0}, occ_ride[2] = {-1, -1};
-      const bool ar_ride = p.tp > 1 && (p.flags & 128u) && !(p.flags & (1u | 8u | 16u | 32u));
+      int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0}, occ_h[2] = {0, 0};
       auto publish = [&](int kk) {
         if (s_abort) return;
         if (p.audit) {      // exactly-once audit: one count per finished unit of work
@@ -627,7 +605,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             for (int i = 0; i < occ_b[kk]; ++i) atomicAdd(p.audit + occ_a[kk] * p.H + occ_h[kk] + i, 1u);
           } else if (occ_mode[kk] == MODE_OPROJ) {
             atomicAdd(p.audit + p.audit_op_base + occ_a[kk], 1u);
-            if (occ_ride[kk] >= 0) atomicAdd(p.audit + p.audit_ar_base + occ_ride[kk] / p.tp, 1u);
           } else if (occ_mode[kk] == MODE_AR) {
             atomicAdd(p.audit + p.audit_ar_base + occ_a[kk] / p.tp, 1u);
           }
@@ -641,10 +618,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           atom_add_release_gpu(p.ctrl + C_FA_DONE, static_cast<uint32_t>(occ_b[kk]));
         } else if (occ_mode[kk] == MODE_OPROJ) {
           publish_ar_ready(p, occ_a[kk]);
-          if (occ_ride[kk] >= 0) {        // the slot that rode along is reduced as well
-            finish_ar_slot(p, occ_ride[kk]);
-            occ_ride[kk] = -1;
-          }
         } else if (occ_mode[kk] == MODE_AR) {
           fence_acq_rel_sys();
           finish_ar_slot(p, occ_a[kk]);
@@ -722,18 +695,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           d[T_FT] = ft; d[TO_BASE] = base_out; d[TO_VNT] = min(p.sg, p.num_out - base_out);
           d[TO_VALID] = min(128, q_len - mb * 128); d[TO_SLOT] = arg;
           occ_a[k] = arg;
-          d[TO_AR_SLOT] = -1;
-          if (mode == MODE_OPROJ && ar_ride) {
-            // The compute warps of an O_proj task mostly wait for the tensor pipe: give
-            // them a ready AllReduce slot of this rank to reduce meanwhile.
-            const int ar_arg = try_claim_ar_queue(p);
-            if (ar_arg >= 0) {
-              const int aft = ar_arg / p.nsg, ag = ar_arg % p.nsg;
-              d[TO_AR_SLOT] = ar_arg; d[TO_AR_FT] = aft; d[TO_AR_BASE] = ag * p.sg;
-              d[TO_AR_VNT] = min(p.sg, p.num_out - ag * p.sg);
-              occ_ride[k] = ar_arg;
-            }
-          }
         }
         d[T_MODE] = mode;
         occ_mode[k] = mode;
@@ -1104,22 +1065,9 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         const int ft = d[T_FT], base_out = d[TO_BASE], vnt = d[TO_VNT], valid_m = d[TO_VALID];
         const bool leader = ((warp & 3) == 0 && lane == 0);
         const uint32_t stg = smem0 + kSmOpStaging + wg * kPanel;   // [128 rows][64 cols] bf16
-        // An AllReduce slot riding along: per pass one batch of reductions goes out before
-        // the wait for the accumulator and is stored right after it, and another goes out
-        // before the epilogue and is stored after it, so the NVLink round trips pass while
-        // the tensor pipe works or the epilogue runs; what is left is done after the last
-        // pass.
-        ArCursor arc{d[TO_AR_FT], d[TO_AR_BASE], tid - 128, 0};
-        if (d[TO_AR_SLOT] >= 0) arc.total = d[TO_AR_VNT] * 2048;
-        uint4 arv[16];
         for (int h = 0; h * 2 < vnt; ++h) {
-          const int ar_n0 = ar_batch_n(p, arc);
-          if (ar_n0) ar_load(p, arc, ar_n0, arv);
           wait_bar(env, smem_u32(&bars.acc_full[h]), acc_par[h], 0xB0 + h);
           acc_par[h] ^= 1u;
-          if (ar_n0) ar_store(p, arc, ar_n0, arv);
-          const int ar_n = ar_batch_n(p, arc);
-          if (ar_n) ar_load(p, arc, ar_n, arv);
           tc_fence_after();
           const int o_t = 2 * h + wg;                   // column tile inside the super-group
           if (o_t < vnt) {
@@ -1179,11 +1127,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars.acc_free[h]));
           }
-          if (ar_n) ar_store(p, arc, ar_n, arv);
-        }
-        if (arc.total) {
-          ar_rest(p, arc);
-          if (lane == 0) __threadfence_system();   // one per warp; the scheduler fences again
         }
         // Ordering towards other CTAs / ranks: the leader waits for its TMA stores, rows
         // written directly get a gpu-scope fence; the one system-scope fence per task is

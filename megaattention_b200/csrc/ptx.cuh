@@ -301,19 +301,24 @@ __device__ __forceinline__ int atom_add_release_sys_s32(int* p, int v) {
                : "memory");
   return o;
 }
-__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 // fire-and-forget add (no value comes back, so the issuing thread does not wait for NVLink)
 __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t atom_cas_acqrel_sys(uint32_t* p, uint32_t cmp, uint32_t v) {
+// 16-byte load at gpu scope (served by L2, where remote atomics on this GPU's memory are
+// performed): used for polling hints only, never as the synchronising access.
+__device__ __forceinline__ uint4 ld_relaxed_gpu_b128(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t atom_or_relaxed_sys(uint32_t* p, uint32_t v) {
   uint32_t o;
-  asm volatile("atom.acq_rel.sys.global.cas.b32 %0, [%1], %2, %3;" : "=r"(o)
-               : "l"(p), "r"(cmp), "r"(v) : "memory");
+  asm volatile("atom.relaxed.sys.global.or.b32 %0, [%1], %2;" : "=r"(o) : "l"(p), "r"(v)
+               : "memory");
   return o;
 }
 __device__ __forceinline__ uint64_t atom_or_acqrel_gpu_u64(uint64_t* p, uint64_t v) {

@@ -70,11 +70,12 @@ def main():
 
     shapes = {"all": REF_SHAPES + BENCH_SHAPES, "ref": REF_SHAPES, "bench": BENCH_SHAPES}[args.shapes]
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    gate = torch.zeros(1, device=dev)
     stream = torch.cuda.current_stream()
     jf = open(args.json, "w") if (args.json and rank == 0) else None
-    ride = _cabi.MA_FLAG_AR_RIDE if world > 1 else 0
+    ded = _cabi.MA_FLAG_AR_DEDICATED
     flag_sets = [0, _cabi.MA_FLAG_DRAIN_FIRST] if world == 1 else \
-        [0, _cabi.MA_FLAG_DRAIN_FIRST, ride, ride | _cabi.MA_FLAG_DRAIN_FIRST]
+        [0, _cabi.MA_FLAG_DRAIN_FIRST, ded, ded | _cabi.MA_FLAG_DRAIN_FIRST]
     rows = []
     for seqlens, H, hidden, kvm in shapes:
         sk = [kvm * s for s in seqlens]
@@ -98,7 +99,8 @@ def main():
             for i in range(1 + iters):
                 flush.zero_()
                 if world > 1:
-                    torch.cuda._sleep(200000)
+                    torch.cuda._sleep(1000000)
+                    dist.all_reduce(gate)      # the ranks leave it together: aligned starts
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(stream); ws.launch(flags=flags); b.record(stream)
                 if i >= 1:

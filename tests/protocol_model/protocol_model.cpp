@@ -7,7 +7,7 @@
 //
 //   attention task counter -> per-row-tile head count -> ordered O_proj ready queue
 //   (reserve / fill / publish in reservation order) -> ticket pop -> owner rank's ready count
-//   (one arrival per rank) -> compare-and-swap claim -> done counters -> count-out exit with
+//   (one arrival per rank, one byte per slot) -> claim by atomic OR of the slot's flag -> done counters -> count-out exit with
 //   full-capacity clear by the last CTA -> phase/sign barrier across the ranks.
 //
 // Every wait is bounded as in the kernel: when the limit passes, the waiter writes a status
@@ -38,7 +38,6 @@ using clk = std::chrono::steady_clock;
 enum { C_FA_COUNTER, C_FA_DONE, C_OP_RESERVE, C_OP_PUBLISH, C_OP_CONSUME, C_OP_DONE, C_AR_DONE, C_QUIESCE, C_NUM };
 enum { ST_OK = 0, ST_TIMEOUT_PUBLISH = 2, ST_TIMEOUT_NVL = 4, ST_TIMEOUT_IDLE = 6 };
 enum { MODE_IDLE, MODE_FA, MODE_OPROJ, MODE_AR, MODE_DONE };
-constexpr uint32_t kClaimed = 0x40000000u;
 
 struct Config {
   int tp = 2, ctas = 6, R = 12, H = 4, nsg = 3, launches = 3, limit_ms = 300;
@@ -102,14 +101,17 @@ bool try_pop_oproj(Rank& r, int total_op, int* pending, int* arg) {
   return true;
 }
 
+// ready counts are packed one byte per slot (bit 7 = claimed), four slots per word, as in
+// the kernel: arrivals add 1 << shift, the claim is an atomic OR of the flag
 bool try_claim_ar(World& w, int rank, int* arg) {
   Rank& r = *w.ranks[rank];
   const int n = w.owned(rank);
   const uint32_t want = static_cast<uint32_t>(w.cfg.tp);
   for (int i = 0; i < n; ++i) {
-    if (r.ready_count[i].load(std::memory_order_relaxed) != want) continue;
-    uint32_t exp = want;
-    if (r.ready_count[i].compare_exchange_strong(exp, want | kClaimed, std::memory_order_acq_rel)) {
+    const int sh = (i & 3) * 8;
+    if (((r.ready_count[i >> 2].load(std::memory_order_relaxed) >> sh) & 0xFFu) != want) continue;
+    const uint32_t old = r.ready_count[i >> 2].fetch_or(0x80u << sh, std::memory_order_acq_rel);
+    if (((old >> sh) & 0xFFu) == want) {
       *arg = i * w.cfg.tp + rank;
       return true;
     }
@@ -188,7 +190,7 @@ void cta_main(World& w, int rank, int cta) {
       r.op_runs[arg].fetch_add(1);
       const int owner = arg % c.tp, idx = arg / c.tp;
       if (!(rank == c.drop_rank && arg == c.drop_slot))           // injected lost arrival
-        w.ranks[owner]->ready_count[idx].fetch_add(1, std::memory_order_release);
+        w.ranks[owner]->ready_count[idx >> 2].fetch_add(1u << ((idx & 3) * 8), std::memory_order_release);
       r.ctrl[C_OP_DONE].fetch_add(1, std::memory_order_release);
     } else {
       r.ar_runs[arg / c.tp].fetch_add(1);

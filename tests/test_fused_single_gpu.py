@@ -237,6 +237,6 @@ def test_stage_flags_that_do_not_fit_the_plan_are_refused():
             ws.launch(flags=flags)
     with pytest.raises(AssertionError):
         ws.launch_ar_only()
-    ws.launch(flags=_cabi.MA_FLAG_AR_RIDE)      # harmless on one rank: nothing to ride
+    ws.launch(flags=_cabi.MA_FLAG_AR_DEDICATED)      # no effect on one rank
     ws.check_status()
     assert ws.ctrl.cpu().tolist() == [0] * 8
