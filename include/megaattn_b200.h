@@ -51,12 +51,6 @@ typedef enum ma_error {
                                   multicast path runs far below the NVLink copy rate).  Same sum:
                                   fp32, rounded once.  No reference counterpart. */
 #define MA_FLAG_TILE_ORDER 4u /* claim attention tasks in row-tile order, ignoring fa_order */
-#define MA_FLAG_AR_DEDICATED 256u /* tp_size > 1: CTAs of the AllReduce role (w_ar of every
-                                 w_fa + w_oproj + w_ar) take only AllReduce slots until every
-                                 slot this rank owns is reduced; the other CTAs reduce only when
-                                 they find no attention or O_proj task.  The reference's roles
-                                 are a bias, never a partition; this makes the AllReduce role
-                                 one.  No reference counterpart. */
 /* ma_launch refuses (MA_ERR_INVALID): more than one of FA_ONLY / AR_ONLY / NO_AR / OPROJ_ONLY;
  * AR_ONLY on one rank or without a multicast address; OPROJ_ONLY with tp_size > 1; AR_P2P unless
  * tp_size == 2 with both peer_csym set; unknown bits. */
@@ -114,8 +108,10 @@ typedef struct ma_plan_desc {
   uint64_t peer_csym[MA_MAX_TP];   /* per-rank addresses of C_sym (symmetric); needed for
                                       MA_FLAG_AR_P2P, may be 0 otherwise.  No reference
                                       counterpart: the reference reduces through multimem only. */
-  uint64_t audit;   /* optional (0 = off): u32[max_row_tiles*H_local + max_total_oproj +
-                       max_owner_slots], zeroed by the caller.  The kernel adds 1 for every
+  uint64_t audit;   /* optional (0 = off; read by the audit build of the library only, see
+                       megaattention_b200/build.py): u32[max_row_tiles*H_local +
+                       max_total_oproj + max_owner_slots], zeroed by the caller.  The kernel
+                       adds 1 for every
                        attention (row tile, head), every O_proj slot and every owned AllReduce
                        slot it finished: after a launch all active entries must read 1
                        (exactly-once check; the reference has none, its status notes ask for

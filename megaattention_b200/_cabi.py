@@ -18,7 +18,6 @@ MA_FLAG_AR_ONLY = 8
 MA_FLAG_NO_AR = 16
 MA_FLAG_OPROJ_ONLY = 32
 MA_FLAG_AR_P2P = 64
-MA_FLAG_AR_DEDICATED = 256
 
 MA_OK = 0
 MA_ERR_INVALID = -1
@@ -84,14 +83,14 @@ class NoAllocArgs(C.Structure):
                 ("out", C.c_uint64), ("status_out", C.POINTER(Status))]
 
 
-def _load():
-    path = _build.LIB
-    if not os.path.exists(path) or _build._stale():
+def _load(path=None, audit=False):
+    path = path or (_build.LIB_AUDIT if audit else _build.LIB)
+    if not os.path.exists(path) or _build._stale(path):
         try:
-            _build.build()     # under a file lock, into a temporary file, then renamed
+            _build.build(audit=audit)     # under a file lock, into a temporary file, then renamed
         except Exception as exc:  # no nvcc on this machine: use what is there, if anything
             if not os.path.exists(path):
-                raise ImportError(f"libmegaattn_b200.so is missing and cannot be built: {exc}")
+                raise ImportError(f"{os.path.basename(path)} is missing and cannot be built: {exc}")
     lib = C.CDLL(path)
     for name in EXPORTS:
         getattr(lib, name)     # AttributeError if the library does not export it
@@ -115,6 +114,16 @@ def _load():
 
 
 lib = _load()
+_audit_lib = None
+
+
+def audit_lib():
+    """The audit build of the library (same ABI, compiled with -DMA_AUDIT: the kernel counts
+    executions per task into ``ma_plan_desc.audit``).  Loaded on first use; tests only."""
+    global _audit_lib
+    if _audit_lib is None:
+        _audit_lib = _load(audit=True)
+    return _audit_lib
 
 
 def strerror(code: int) -> str:

@@ -230,7 +230,11 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   k.cache_seqlens = reinterpret_cast<const int*>(d->cache_seqlens);
   k.pps = d->max_pages_per_seq;
   k.status = reinterpret_cast<uint32_t*>(d->status);
+#ifdef MA_AUDIT
   k.audit = reinterpret_cast<uint32_t*>(d->audit);
+#else
+  if (d->audit) { delete pl; return MA_ERR_INVALID; }     // counters need the audit build
+#endif
   k.audit_op_base = d->max_row_tiles * d->H_local;
   k.audit_ar_base = k.audit_op_base + static_cast<int>(max_total);
   k.csym_mc = d->csym_multicast;
@@ -269,7 +273,7 @@ int ma_launch(ma_plan* pl, const ma_launch_args* a, void* stream) {
       (kp.tp != 2 || !pl->desc.peer_csym[0] || !pl->desc.peer_csym[1]))
     return MA_ERR_INVALID;
   if (kp.flags & ~(MA_FLAG_FA_ONLY | MA_FLAG_DRAIN_FIRST | MA_FLAG_TILE_ORDER | MA_FLAG_AR_ONLY |
-                   MA_FLAG_NO_AR | MA_FLAG_OPROJ_ONLY | MA_FLAG_AR_P2P | MA_FLAG_AR_DEDICATED))
+                   MA_FLAG_NO_AR | MA_FLAG_OPROJ_ONLY | MA_FLAG_AR_P2P))
     return MA_ERR_INVALID;
   if (kp.w_fa < 0 || kp.w_oproj < 0 || kp.w_ar < 0 || kp.w_fa + kp.w_oproj + kp.w_ar < 1)
     return MA_ERR_INVALID;

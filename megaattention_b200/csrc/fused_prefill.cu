@@ -258,13 +258,7 @@ __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, i
   // three orders).  With the "drain first" launch flag downstream work goes first so that
   // AllReduce traffic starts early and keeps flowing: roles 0/1 become 3: OPROJ,FA,AR and
   // role 2 becomes 4: AR,OPROJ,FA.
-  // With the "dedicated" launch flag the AllReduce-role CTAs take nothing but AllReduce
-  // slots until every slot this rank owns is reduced: NVLink round trips and the fences
-  // that wait for them then stay on those SMs and off the ones doing tensor work.
-  const bool ar_only_cta = (p.flags & 256u) && p.tp > 1 && (role == 2 || role == 4) &&
-                           !(p.flags & 16u) &&
-                           static_cast<int>(ld_relaxed_gpu(p.ctrl + C_AR_DONE)) < local_owned;
-  for (int i = 0; i < (ar_only_cta ? 1 : 3); ++i) {
+  for (int i = 0; i < 3; ++i) {
     int m;
     if (role == 3) m = (i == 0) ? MODE_OPROJ : (i == 1) ? MODE_FA : MODE_AR;
     else if (role == 4) m = MODE_AR - i;
@@ -407,77 +401,67 @@ __device__ __forceinline__ void stage_row32(uint32_t panel, int row, int col0,
 }
 
 // ---------------------------------------------------------------- AllReduce of one slot
-// A slot is 128 rows x (vnt x 128) bf16 columns = vnt x 2048 chunks of 16 bytes.  The 256
-// compute threads walk it in batches; in a batch every thread first issues all its loads
-// (up to 16 requests of 16 bytes, nothing waits in between: NVLink round trips are
-// microseconds) and then stores the results.
-//   multimem path: 16 (or, for the last odd column tile, 8) multimem.ld_reduce per thread
-//     (fp32 sum of all ranks' bf16 taken in the switch), then multimem.st to every rank;
-//   peer path (MA_FLAG_AR_P2P, two ranks): 8 chunks per thread, the peer's and this rank's
-//     partial loaded with plain 16-byte loads, added in fp32, rounded once, written to both
-//     copies.  With two GPUs the multicast path runs far below the NVLink copy rate.
-constexpr int kArThreads = 256;
-struct ArCursor {
-  int ft, base_out, c0, total;     // c0: this thread's first chunk of the next batch
-};
-__device__ __forceinline__ size_t ar_chunk_elem(const KParams& p, const ArCursor& a, int c) {
-  const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
-  return ((static_cast<size_t>(a.ft * 128 + m) * p.num_out + a.base_out + o_t) * 128) + nc * 8;
+// One AllReduce slot: 128 rows x (vnt x 128) bf16 columns, reduced in the switch and
+// written back to every rank.  `nthr` threads cooperate; each keeps U 16-byte reductions in
+// flight before its first store (NVLink round trips are microseconds).
+template <int U>
+__device__ __forceinline__ void ar_batch(const KParams& p, int ft, int base_out, int c0, int nthr) {
+  auto chunk_addr = [&](int c) -> unsigned long long {
+    const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
+    const size_t elem =
+        ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
+    return p.csym_mc + elem * 2;
+  };
+  uint4 v[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) v[u] = multimem_ld_reduce_bf16x8(chunk_addr(c0 + u * nthr));
+#pragma unroll
+  for (int u = 0; u < U; ++u) multimem_st_b128(chunk_addr(c0 + u * nthr), v[u]);
 }
-// Chunks per thread of the next batch: 16 / 8 / 0 (multimem), 8 / 0 (peer path).
-__device__ __forceinline__ int ar_batch_n(const KParams& p, const ArCursor& a) {
-  if (!(p.flags & 64u) && a.c0 + kArThreads * 15 < a.total) return 16;
-  return (a.c0 + kArThreads * 7 < a.total) ? 8 : 0;
-}
-__device__ __forceinline__ void ar_load(const KParams& p, const ArCursor& a, int n, uint4 (&v)[16]) {
-  if (p.flags & 64u) {
-    const unsigned long long mine = p.peer_csym[p.rank], peer = p.peer_csym[p.rank ^ 1];
+
+// The same batch with plain peer loads and stores, two ranks only: the owner reads its own
+// and the peer's partial, adds in fp32, rounds once and writes both copies.  With two GPUs
+// the multicast path is several times slower than the NVLink copy rate; this one is not.
+template <int U>
+__device__ __forceinline__ void ar_batch_p2p(const KParams& p, int ft, int base_out, int c0, int nthr) {
+  auto chunk_off = [&](int c) -> unsigned long long {
+    const int o_t = c >> 11, m = (c >> 4) & 127, nc = c & 15;
+    const size_t elem =
+        ((static_cast<size_t>(ft * 128 + m) * p.num_out + base_out + o_t) * 128) + nc * 8;
+    return elem * 2;
+  };
+  const unsigned long long mine = p.peer_csym[p.rank], peer = p.peer_csym[p.rank ^ 1];
+  uint4 a[U], b[U];
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
-      v[u] = ld_relaxed_sys_b128(peer + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2);
+  for (int u = 0; u < U; ++u) b[u] = ld_relaxed_sys_b128(peer + chunk_off(c0 + u * nthr));
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
-      v[8 + u] = ld_relaxed_gpu_b128(reinterpret_cast<const void*>(mine + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2));   // this GPU's own partial
-  } else if (n == 16) {
+  for (int u = 0; u < U; ++u)      // this GPU's own partial: gpu scope is enough
+    a[u] = ld_relaxed_gpu_b128(reinterpret_cast<const void*>(mine + chunk_off(c0 + u * nthr)));
 #pragma unroll
-    for (int u = 0; u < 16; ++u)
-      v[u] = multimem_ld_reduce_bf16x8(p.csym_mc + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2);
-  } else {
-#pragma unroll
-    for (int u = 0; u < 8; ++u)
-      v[u] = multimem_ld_reduce_bf16x8(p.csym_mc + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2);
+  for (int u = 0; u < U; ++u) {
+    uint4 r;
+    r.x = add_bf16x2_via_f32(a[u].x, b[u].x); r.y = add_bf16x2_via_f32(a[u].y, b[u].y);
+    r.z = add_bf16x2_via_f32(a[u].z, b[u].z); r.w = add_bf16x2_via_f32(a[u].w, b[u].w);
+    const unsigned long long off = chunk_off(c0 + u * nthr);
+    st_relaxed_sys_b128(peer + off, r);
+    st_relaxed_sys_b128(mine + off, r);
   }
 }
-__device__ __forceinline__ void ar_store(const KParams& p, ArCursor& a, int n, const uint4 (&v)[16]) {
-  if (p.flags & 64u) {
-    const unsigned long long mine = p.peer_csym[p.rank], peer = p.peer_csym[p.rank ^ 1];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      uint4 r;
-      r.x = add_bf16x2_via_f32(v[8 + u].x, v[u].x); r.y = add_bf16x2_via_f32(v[8 + u].y, v[u].y);
-      r.z = add_bf16x2_via_f32(v[8 + u].z, v[u].z); r.w = add_bf16x2_via_f32(v[8 + u].w, v[u].w);
-      const unsigned long long off = ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2;
-      st_relaxed_sys_b128(peer + off, r);
-      st_relaxed_sys_b128(mine + off, r);
-    }
-  } else if (n == 16) {
-#pragma unroll
-    for (int u = 0; u < 16; ++u)
-      multimem_st_b128(p.csym_mc + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2, v[u]);
-  } else {
-#pragma unroll
-    for (int u = 0; u < 8; ++u)
-      multimem_st_b128(p.csym_mc + ar_chunk_elem(p, a, a.c0 + u * kArThreads) * 2, v[u]);
+
+// One AllReduce slot: 128 rows x (vnt x 128) bf16 columns, reduced in the switch and
+// written back to every rank.  `nthr` (256) threads cooperate; each keeps 16 16-byte
+// reductions in flight before its first store (NVLink round trips are microseconds).  A
+// slot is vnt x 2048 chunks: whole batches of nthr x 16, then one of nthr x 8 if vnt is odd.
+__device__ __forceinline__ void ar_slot(const KParams& p, int ft, int base_out, int vnt, int t,
+                                        int nthr) {
+  const int total = vnt * 2048;
+  int c0 = t;
+  if (p.flags & 64u) {      // MA_FLAG_AR_P2P (host side admits it at tp == 2 only)
+    for (; c0 + nthr * 7 < total; c0 += nthr * 8) ar_batch_p2p<8>(p, ft, base_out, c0, nthr);
+    return;
   }
-  a.c0 += kArThreads * n;
-}
-// A whole slot, batch after batch.
-__device__ __forceinline__ void ar_rest(const KParams& p, ArCursor& a) {
-  uint4 v[16];
-  for (int n = ar_batch_n(p, a); n > 0; n = ar_batch_n(p, a)) {
-    ar_load(p, a, n, v);
-    ar_store(p, a, n, v);
-  }
+  for (; c0 + nthr * 15 < total; c0 += nthr * 16) ar_batch<16>(p, ft, base_out, c0, nthr);
+  if (c0 + nthr * 7 < total) ar_batch<8>(p, ft, base_out, c0, nthr);
 }
 
 }  // namespace
@@ -597,10 +581,14 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
       bool ld_pending[2] = {false, false}, ld_skip[2] = {false, false};
       int pending_ticket = -1;
       uint32_t poll_no = 0;
-      int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0}, occ_h[2] = {0, 0};
+      int occ_mode[2] = {0, 0}, occ_a[2] = {0, 0}, occ_b[2] = {0, 0};
+#ifdef MA_AUDIT
+      int occ_h[2] = {0, 0};
+#endif
       auto publish = [&](int kk) {
         if (s_abort) return;
-        if (p.audit) {      // exactly-once audit: one count per finished unit of work
+#ifdef MA_AUDIT
+        if (p.audit) {      // exactly-once audit (audit build only): one count per finished unit
           if (occ_mode[kk] == MODE_FA) {
             for (int i = 0; i < occ_b[kk]; ++i) atomicAdd(p.audit + occ_a[kk] * p.H + occ_h[kk] + i, 1u);
           } else if (occ_mode[kk] == MODE_OPROJ) {
@@ -609,6 +597,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             atomicAdd(p.audit + p.audit_ar_base + occ_a[kk] / p.tp, 1u);
           }
         }
+#endif
         if (occ_mode[kk] == MODE_FA) {
           fence_acq_rel_gpu();
           const uint32_t old = atom_add_acqrel_gpu(p.head_ready + occ_a[kk],
@@ -686,7 +675,10 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
           d[TF_QROW0] = q0 + mb * 128; d[TF_VALID] = min(128, q_len - mb * 128);
           d[TF_KSTART] = k0; d[TF_KLEN] = k_len; d[TF_OFFSET] = offset; d[TF_NBLK] = nblk;
           d[TF_MB] = mb;
-          occ_a[k] = ft; occ_b[k] = nt; occ_h[k] = head0;
+          occ_a[k] = ft; occ_b[k] = nt;
+#ifdef MA_AUDIT
+          occ_h[k] = head0;
+#endif
         } else if (mode == MODE_OPROJ || mode == MODE_AR) {
           const int ft = arg / p.nsg, g = arg % p.nsg;
           const int base_out = g * p.sg;
@@ -1138,8 +1130,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         }
         if (valid_m != 128) __threadfence();
       } else if (mode == MODE_AR) {
-        ArCursor arc{d[T_FT], d[TO_BASE], tid - 128, d[TO_VNT] * 2048};
-        ar_rest(p, arc);
+        ar_slot(p, d[T_FT], d[TO_BASE], d[TO_VNT], tid - 128, 256);
         if (lane == 0) __threadfence_system();   // one per warp; the scheduler fences again
       }
       __syncwarp();

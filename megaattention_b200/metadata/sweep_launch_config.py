@@ -73,9 +73,7 @@ def main():
     gate = torch.zeros(1, device=dev)
     stream = torch.cuda.current_stream()
     jf = open(args.json, "w") if (args.json and rank == 0) else None
-    ded = _cabi.MA_FLAG_AR_DEDICATED
-    flag_sets = [0, _cabi.MA_FLAG_DRAIN_FIRST] if world == 1 else \
-        [0, _cabi.MA_FLAG_DRAIN_FIRST, ded, ded | _cabi.MA_FLAG_DRAIN_FIRST]
+    flag_sets = [0, _cabi.MA_FLAG_DRAIN_FIRST]
     rows = []
     for seqlens, H, hidden, kvm in shapes:
         sk = [kvm * s for s in seqlens]

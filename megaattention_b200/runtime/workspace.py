@@ -58,6 +58,7 @@ class FusedFaOprojArWorkspace:
     def __init__(self, **kw):
         self.__dict__.update(kw)
         self._plan = None
+        self._lib = _cabi.lib
         self._args = None
         self._meta = None
         self.default_flags = 0   # OR of _cabi.MA_FLAG_* applied by launch()
@@ -191,8 +192,10 @@ class FusedFaOprojArWorkspace:
         AllReduce slot; see ``audit_counts``) for exactly-once checks.
         """
         if self._plan is not None:
-            _cabi.lib.ma_plan_destroy(self._plan)
+            self._lib.ma_plan_destroy(self._plan)
             self._plan = None
+        # the execution counters exist in the audit build of the library only
+        self._lib = _cabi.audit_lib() if audit else _cabi.lib
         d = _cabi.PlanDesc()
         d.device = self.dev.index if self.dev.index is not None else torch.cuda.current_device()
         d.tp_size, d.rank = self.tp_size, self.rank
@@ -231,7 +234,7 @@ class FusedFaOprojArWorkspace:
             d.peer_nvl_signal[r] = self.nvl_peer_ptrs[r]
             d.peer_csym[r] = self.csym_peer_ptrs[r]
         plan = C.c_void_p()
-        _cabi.check(_cabi.lib.ma_plan_create(C.byref(d), C.byref(plan)), "ma_plan_create")
+        _cabi.check(self._lib.ma_plan_create(C.byref(d), C.byref(plan)), "ma_plan_create")
         self._plan = plan
         self._args = _cabi.LaunchArgs(int(w_fa), int(w_oproj), int(w_ar),
                                       int(num_ctas) if num_ctas else 0, 0)
@@ -317,7 +320,7 @@ class FusedFaOprojArWorkspace:
             assert tuple(K.shape[1:]) == (self.H_kv, self.D) == tuple(V.shape[1:])
             tot_k = K.shape[0]
             assert int(meta.cu_seqlens_k[-1]) == tot_k
-        _cabi.check(_cabi.lib.ma_plan_set_inputs(
+        _cabi.check(self._lib.ma_plan_set_inputs(
             self._plan, Q.data_ptr(), K.data_ptr(), V.data_ptr(), W_o.data_ptr(),
             int(Q.shape[0]), int(tot_k), int(W_o.shape[1])), "ma_plan_set_inputs")
         self._bound = (Q, K, V, W_o)          # keep them alive
@@ -331,7 +334,7 @@ class FusedFaOprojArWorkspace:
         if getattr(self, "_bound", None) is not None:
             kv = (self.K_cache, self.V_cache) if self.paged else (self.K, self.V)
             tot_k = self.max_num_pages * 128 if self.paged else self.max_tot_k
-            _cabi.check(_cabi.lib.ma_plan_set_inputs(
+            _cabi.check(self._lib.ma_plan_set_inputs(
                 self._plan, self.Q.data_ptr(), kv[0].data_ptr(), kv[1].data_ptr(),
                 self.W_o.data_ptr(), self.tot_cap, tot_k, self.hidden_pad), "ma_plan_set_inputs")
             self._bound = None
@@ -382,7 +385,7 @@ class FusedFaOprojArWorkspace:
             flags |= _cabi.MA_FLAG_AR_P2P
         args = _cabi.LaunchArgs(self._args.w_fa, self._args.w_oproj, self._args.w_ar,
                                 self._args.num_ctas, int(flags))
-        _cabi.check(_cabi.lib.ma_launch(self._plan, C.byref(args),
+        _cabi.check(self._lib.ma_launch(self._plan, C.byref(args),
                                         C.c_void_p(self._ts.cuda_stream)), "ma_launch")
 
     def launch_fa_only(self):
@@ -416,7 +419,7 @@ class FusedFaOprojArWorkspace:
     def check_status(self):
         """Synchronise the launch stream and raise if a device-side wait gave up."""
         st = _cabi.Status()
-        rc = _cabi.lib.ma_read_status(self._plan, C.c_void_p(self._ts.cuda_stream), C.byref(st))
+        rc = self._lib.ma_read_status(self._plan, C.c_void_p(self._ts.cuda_stream), C.byref(st))
         if rc != _cabi.MA_OK:
             raise RuntimeError(
                 f"fused prefill kernel: {_cabi.strerror(rc)} "
@@ -446,7 +449,7 @@ class FusedFaOprojArWorkspace:
     def __del__(self):
         try:
             if self._plan is not None:
-                _cabi.lib.ma_plan_destroy(self._plan)
+                self._lib.ma_plan_destroy(self._plan)
                 self._plan = None
         except Exception:
             pass

@@ -131,13 +131,11 @@ def main():
         q_per_kv=QPK, max_tot_k=1536, device=dev)
     ws.compile(w_fa=2, w_oproj=1, w_ar=1, num_ctas=int(os.environ.get("MA_TEST_CTAS", "24")))
     # Every scheduling variant runs the whole layer sequence on the same workspace: the
-    # reference's role bias, downstream work first, AllReduce-role CTAs that do nothing
-    # else, and with two ranks the reduction through multimem as well as through peer loads.
-    variants = [("roles", 0, True), ("drain-first", _cabi.MA_FLAG_DRAIN_FIRST, True),
-                ("dedicated", _cabi.MA_FLAG_AR_DEDICATED, True),
-                ("dedicated+drain", _cabi.MA_FLAG_AR_DEDICATED | _cabi.MA_FLAG_DRAIN_FIRST, True)]
+    # reference's role bias and downstream work first, and with two ranks the reduction
+    # through multimem as well as through peer loads.
+    variants = [("roles", 0, True), ("drain-first", _cabi.MA_FLAG_DRAIN_FIRST, True)]
     if world == 2:
-        variants += [("multimem", 0, False), ("multimem dedicated", _cabi.MA_FLAG_AR_DEDICATED, False)]
+        variants += [("multimem", 0, False), ("multimem drain-first", _cabi.MA_FLAG_DRAIN_FIRST, False)]
     worst = 0.0
     for tag, flags, p2p in variants:
         ws.default_flags, ws.ar_p2p = flags, p2p
@@ -157,7 +155,7 @@ def main():
     ws.launch(); ws.check_status()
     dist.barrier()
     if os.environ.get("MA_TEST_C3", "1") == "1":
-        for flags in (0, _cabi.MA_FLAG_AR_DEDICATED | _cabi.MA_FLAG_DRAIN_FIRST):
+        for flags in (0, _cabi.MA_FLAG_DRAIN_FIRST):
             worst = max(worst, run_c3(group, rank, world, dev, flags, True))
         dist.barrier()
     print(f"[rank {rank}] ALL OK worst err_comp={worst:.3g}", flush=True)

