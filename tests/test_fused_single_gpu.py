@@ -216,8 +216,8 @@ def test_kernel_error_is_the_floor_of_its_staging(name):
     got_o = torch.cat([res["oscr"][t, :vm] for t, (s0, vm) in enumerate(tiles)])
     # (the kernel moves its reference maximum lazily, the model at every block: P is rounded
     # at a different scale, so equality of the bits is the common case, not a law)
-    for got, want, what, min_equal in ((got_o, Om.float(), "O_scratch", 0.5),
-                                       (res["out"].float(), Ym.float(), "output", 0.5)):
+    for got, want, what, min_equal in ((got_o, Om.float(), "O_scratch", 0.3),
+                                       (res["out"].float(), Ym.float(), "output", 0.3)):
         d = (got - want).abs()
         equal = float((d == 0).float().mean())
         worst = float(d.max() / want.abs().max())
