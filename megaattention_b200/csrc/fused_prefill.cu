@@ -69,12 +69,6 @@ struct Bars {
   uint64_t acc_full[2];     // MMA: O_proj accumulator half h complete
   uint64_t acc_free[2];     // epilogue warps: half h read out (count 8)
   uint64_t drain[2];        // abort path only: an issuer's outstanding MMAs have retired
-  uint64_t spare;           // never waited on.  It fixes where the words that follow this struct
-                            // in shared memory land (the issuers' lock, the abort flag, the
-                            // task descriptors): without it the attention stage measured 2.5 %
-                            // slower (0.1597 vs 0.1560 ms on one box, twice), presumably
-                            // because a word that is spun on then shares an atomic unit with a
-                            // hot barrier
 };
 
 struct Env {
@@ -489,11 +483,17 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
                      const __grid_constant__ CUtensorMap tmC,
                      const __grid_constant__ KParams p) {
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ __align__(8) Bars bars;
+  // The words that threads spin on (the abort flag is read in every wait loop, the issuers'
+  // lock is hammered with atomics) get 128-byte lines of their own, away from the mbarriers:
+  // where the compiler put them next to the barrier block by default depended on the
+  // block's size, and one such placement cost the attention stage 2.5 % (0.1597 vs 0.1560 ms).
+  __shared__ __align__(128) Bars bars;
   __shared__ uint32_t s_tmem;
-  __shared__ int s_abort;
-  __shared__ int s_desc[2][T_WORDS];
-  __shared__ int s_pipe_turn;   // serialises the two issuers' MMA batches (scheduling only)
+  __shared__ __align__(128) int s_abort_line[32];
+  __shared__ __align__(128) int s_desc[2][T_WORDS];
+  __shared__ __align__(128) int s_pipe_line[32];
+  int& s_abort = s_abort_line[0];
+  int& s_pipe_turn = s_pipe_line[0];   // serialises the two issuers' MMA batches (scheduling only)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -527,7 +527,6 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     }
     mbar_init(smem_u32(&bars.drain[0]), 1);
     mbar_init(smem_u32(&bars.drain[1]), 1);
-    mbar_init(smem_u32(&bars.spare), 1);
     fence_mbar_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
