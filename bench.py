@@ -34,7 +34,8 @@ import torch  # noqa: E402
 from megaattention_b200.workloads import (  # noqa: E402
     WORKLOADS, make_rank_inputs, fa_flops, oproj_flops, ar_bytes)
 from megaattention_b200.metadata import build_row_desc, choose_launch_config  # noqa: E402
-from megaattention_b200.metadata.launch_heuristic import launch_flags_b200  # noqa: E402
+from megaattention_b200.metadata.launch_heuristic import (  # noqa: E402
+    launch_flags_b200, fa_prime_tiles_b200)
 
 METRIC = "fused_fa_oproj_ar_prefill_tflops"
 UNIT = "TFLOP/s"
@@ -244,6 +245,8 @@ def main():
     ap.add_argument("--w", type=str, default=None, help="w_fa,w_oproj,w_ar")
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--flags", type=int, default=None, help="launch flags (MA_FLAG_* bits)")
+    ap.add_argument("--prime", type=int, default=None,
+                    help="shortest row tiles whose attention is claimed first (workspace.fa_prime_tiles)")
     ap.add_argument("--stage", default="fused", choices=["fused", "fa", "ar", "oproj", "noar"],
                     help="time one stage of the kernel alone (what the profiles/ captures ran)")
     args = ap.parse_args()
@@ -285,6 +288,7 @@ def main():
     if args.w:
         w = tuple(int(x) for x in args.w.split(","))
     flags = args.flags if args.flags is not None else launch_flags_b200(meta, wl.hidden, tp, h)
+    prime = args.prime if args.prime is not None else fa_prime_tiles_b200(meta, wl.hidden, tp, h)
 
     def make_ws():
         x = FusedFaOprojArWorkspace.create(
@@ -293,6 +297,7 @@ def main():
             max_num_batch=meta.num_batch, max_tot_k=wl.tot_k, device=dev)
         x.compile(w_fa=w[0], w_oproj=w[1], w_ar=w[2], num_ctas=args.ctas or None)
         x.default_flags = flags
+        x.fa_prime_tiles = prime
         return x
 
     ws = make_ws()
@@ -547,6 +552,7 @@ def main():
             "config": {"workload": workload_name(wl, tp) + stage_note, "seqlens_q": wl.seqlens_q,
                        "kv_mult": wl.kv_mult, "H_local": h, "H_kv": hkv, "hidden": wl.hidden,
                        "role_weights": list(w), "sg": cfg.sg, "launch_flags": flags,
+                       "fa_prime_tiles": prime,
                        "l2": "512 MiB buffer written before every timed launch"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": K,
             "clocks": clocks, "unfused": unfused, "parity": parity, "scaling_anchor": anchor,

@@ -40,7 +40,8 @@ def claim_order(meta, prime: int = 0) -> np.ndarray:
     ``prime`` > 0 moves that many of the shortest row tiles to the front: their attention
     finishes within microseconds, so O_proj and AllReduce work exists almost from the start
     of the launch instead of only after the first long attention task (tens of
-    microseconds) — worth it when the launch is bound by the AllReduce."""
+    microseconds) — worth it when the launch is bound by the AllReduce.  ``prime`` < 0
+    interleaves long and short row tiles instead (see below)."""
     M = meta.M_TILE
     b = meta.batch_idx.astype(np.int64)
     lq = np.diff(meta.cu_seqlens_q.astype(np.int64))[b]
@@ -48,7 +49,17 @@ def claim_order(meta, prime: int = 0) -> np.ndarray:
     last_row = (meta.m_block.astype(np.int64) + 1) * M + (lk - lq)
     nblk = np.minimum(-(-lk // M), -(-last_row // M))
     order = np.argsort(-nblk, kind="stable").astype(np.int32)
-    prime = int(min(max(prime, 0), order.size))
+    if prime < 0:
+        # interleaved: longest, shortest, second longest, second shortest, ...  Row tiles
+        # then finish at an even rate from the start of the launch (steady O_proj and
+        # AllReduce work) while the long tasks still start early; the last tasks claimed are
+        # of middling length.
+        out = np.empty_like(order)
+        half = (order.size + 1) // 2
+        out[0::2] = order[:half]
+        out[1::2] = order[half:][::-1]
+        return out
+    prime = int(min(prime, order.size))
     if prime:
         order = np.concatenate([order[order.size - prime:][::-1], order[:order.size - prime]])
     return order

@@ -95,6 +95,7 @@ def run_c3(group, rank, world, dev, flags, p2p):
         max_tot_k=wl.tot_k, device=dev)
     ws.compile(w_fa=cfg.w_fa, w_oproj=cfg.w_oproj, w_ar=cfg.w_ar)
     ws.default_flags, ws.ar_p2p = flags, p2p
+    ws.fa_prime_tiles = -1 if flags else 0      # interleaved claim order with "drain first"
     ws.set_layer(meta, Q.to(dev), K.to(dev), V.to(dev), W.to(dev))
     for _ in range(2):                      # the second launch starts from the first one's exit state
         ws.launch()
@@ -139,6 +140,7 @@ def main():
     worst = 0.0
     for tag, flags, p2p in variants:
         ws.default_flags, ws.ar_p2p = flags, p2p
+        ws.fa_prime_tiles = {0: 0, 1: -1, 2: 3}[len(tag) % 3]      # every claim order gets a turn
         worst = max(worst, run_layers(ws, rank, world, dev, tag))
     # over-capacity layers: AssertionError before anything is touched, workspace stays usable
     for sq, sk in (([1537], None), ([256], [1537])):

@@ -156,3 +156,6 @@ def test_claim_order_is_longest_first_with_optional_priming():
     rest = [nblk[t] for t in primed[3:]]
     assert rest == sorted(rest, reverse=True)
     assert claim_order(meta, prime=10 ** 6).tolist() == order[::-1].tolist()
+    mixed = claim_order(meta, prime=-1)          # longest, shortest, 2nd longest, ...
+    assert sorted(mixed.tolist()) == list(range(meta.num_row_tiles))
+    assert mixed[0] == order[0] and mixed[1] == order[-1] and mixed[2] == order[1]
