@@ -103,7 +103,12 @@ typedef struct ma_plan_desc {
   int32_t max_pages_per_seq;
   int32_t reserved0;
   uint64_t fa_order;   /* i32[max_row_tiles]: row tiles in the order attention tasks are
-                          claimed (the workspace sorts longest-first); 0 = natural order.
+                          claimed; 0 = natural order.  Any permutation of the active row
+                          tiles is valid: the order only shapes the schedule.  The Python
+                          workspace writes longest-first (one GPU, small AllReduce share),
+                          or long and short tiles alternating so that row tiles complete,
+                          and their AllReduce slots become ready, from the start of the
+                          launch (runtime/workspace.py, claim_order).
                           No reference counterpart: the reference claims in tile order. */
   uint64_t peer_csym[MA_MAX_TP];   /* per-rank addresses of C_sym (symmetric); needed for
                                       MA_FLAG_AR_P2P, may be 0 otherwise.  No reference

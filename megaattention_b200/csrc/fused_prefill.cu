@@ -215,8 +215,8 @@ __device__ __noinline__ int try_claim_ar(const KParams& p, int local_owned, uint
 }
 
 __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, int total_op,
-                                           int local_owned, uint32_t poll_no, int* pending,
-                                           int* mode, int* arg) {
+                                           int local_owned, uint32_t poll_no, bool busy,
+                                           int* pending, int* mode, int* arg) {
   const KParams& p = *e.p;
   *mode = MODE_IDLE;
   *arg = -1;
@@ -270,8 +270,12 @@ __device__ __noinline__ void schedule_pick(const Env& e, int role, int num_fa, i
     if (m == MODE_FA) ok = try_fa(p, num_fa, arg);
     else if (fa_only) ok = false;
     else if (m == MODE_OPROJ) ok = try_pop_oproj(p, total_op, pending, arg);
-    else if (p.tp > 1 && !(p.flags & 16u))
+    else if (p.tp > 1 && !(p.flags & 16u) &&
+             !(busy && static_cast<int>(ld_relaxed_gpu(p.ctrl + C_OP_CONSUME)) >= total_op))
     {
+      // (once every O_proj task has been handed out only reductions are left and CTAs go
+      // idle: a CTA that still has a task running leaves ready slots to them instead of
+      // queueing one behind its own)
       const int q = try_claim_ar(p, local_owned, poll_no);
       if (q >= 0) { *arg = q; ok = true; }
     }
@@ -639,8 +643,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         int mode, arg;
         uint64_t idle_t0 = 0;
         while (true) {
-          schedule_pick(env, role, num_fa, total_op, local_owned, poll_no++, &pending_ticket,
-                        &mode, &arg);
+          schedule_pick(env, role, num_fa, total_op, local_owned, poll_no++, occupied[k ^ 1],
+                        &pending_ticket, &mode, &arg);
           if (mode != MODE_IDLE) break;
           // nothing to do and not finished: bounded like every other wait (a rank that
           // never shows up, or counts that can never be reached, must not hang the GPU)
