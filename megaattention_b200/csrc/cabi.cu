@@ -206,6 +206,7 @@ int ma_plan_create(const ma_plan_desc* d, ma_plan** out) {
   const float scale = d->softmax_scale > 0.f ? d->softmax_scale : 0.08838834764831845f;
   k.scale_log2 = scale * 1.4426950408889634f;
   k.pair = (k.q_per_kv % 2 == 0) ? 1 : 0;
+  k.sep = (!k.pair && k.H >= 2) ? 1 : 0;
   k.max_row_tiles = d->max_row_tiles;
   const long long max_total = static_cast<long long>(d->max_row_tiles) * k.nsg;
   k.max_owner_slots = static_cast<int>((max_total + d->tp_size - 1) / d->tp_size);

@@ -24,9 +24,12 @@
 //   warp 3 (lane 0)  MMA issuer of attention tile 1
 //   warps 4-7, 8-11  two compute warpgroups: online softmax (one thread per row), both
 //                    epilogues, AllReduce slots
-// When q heads come in pairs that share a kv head, an FA task is two q heads of one row
-// tile: both tiles use the same K/V stages and the two compute warpgroups alternate, so
-// the tensor pipe runs one tile's MMAs under the other tile's softmax.
+// An FA task is two q heads of one row tile whenever the rank has two: the two compute
+// warpgroups alternate, so the tensor pipe runs one tile's MMAs under the other tile's
+// softmax.  With an even number of q heads per kv head the two heads share a kv head and
+// every K/V stage of the ring; otherwise (MHA included) each head gets K/V stages of its
+// own in the same ring (K of both heads, then V of both heads, per key block), and the
+// head an odd count leaves over runs alone.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -59,7 +62,8 @@ struct Bars {
   uint64_t q_full[2];       // TMA: Q tile i landed
   uint64_t q_empty[2];      // MMA: last Q K^T of tile i done + epilogue: staging released (count 2)
   uint64_t kv_full[kKvSlots];
-  uint64_t kv_empty[kKvSlots];   // both MMA issuers release a slot (count 2)
+  uint64_t kv_empty[kKvSlots];   // shared K/V stages: both MMA issuers release a slot (count 2);
+                                 // separate stages: the one issuer that reads it (count 1)
   uint64_t s_full[2];       // MMA: S_i ready
   uint64_t p_full[2];       // softmax warps: P_i written (count 4, one arrival per warp)
   uint64_t o_done[2];       // MMA: last P V of the task for tile i completed
@@ -110,6 +114,17 @@ __device__ __forceinline__ bool wait_bar(const Env& e, uint32_t bar, uint32_t pa
 
 // ---------------------------------------------------------------- scheduler (thread 0)
 __device__ __forceinline__ bool try_fa(const KParams& p, int num_fa, int* arg) {
+  if (p.sep) {
+    // two heads per task, the last head of an odd count alone: the counter numbers tasks,
+    // (H + 1) / 2 per row tile; arg stays position * H + first head
+    const int hp = (p.H + 1) >> 1;
+    const int n_tasks = (num_fa / p.H) * hp;
+    if (static_cast<int>(ld_relaxed_gpu(p.ctrl + C_FA_COUNTER)) < n_tasks) {
+      const int id = static_cast<int>(atom_add_relaxed_gpu(p.ctrl + C_FA_COUNTER, 1u));
+      if (id < n_tasks) { *arg = (id / hp) * p.H + 2 * (id % hp); return true; }
+    }
+    return false;
+  }
   const uint32_t step = p.pair ? 2u : 1u;
   if (static_cast<int>(ld_relaxed_gpu(p.ctrl + C_FA_COUNTER)) < num_fa) {
     const uint32_t id = atom_add_relaxed_gpu(p.ctrl + C_FA_COUNTER, step);
@@ -523,7 +538,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
     }
     for (int i = 0; i < kKvSlots; ++i) {
       mbar_init(smem_u32(&bars.kv_full[i]), 1);
-      mbar_init(smem_u32(&bars.kv_empty[i]), 2);
+      mbar_init(smem_u32(&bars.kv_empty[i]), p.sep ? 1 : 2);   // issuers that consume a slot
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&bars.op_full[i]), 1);
@@ -668,8 +683,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         }
         int* d = s_desc[k];
         if (mode == MODE_FA) {
-          const int nt = p.pair ? 2 : 1;
           const int pos = arg / p.H, head0 = arg % p.H;
+          const int nt = p.pair ? 2 : (p.sep ? min(2, p.H - head0) : 1);
           const int ft = (p.fa_order && !(p.flags & 4u)) ? p.fa_order[pos] : pos;
           const int b = p.fa_b[ft], mb = p.fa_mb[ft];
           const int q0 = p.cu_q[b], q_len = p.cu_q[b + 1] - q0;
@@ -728,19 +743,24 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             mbar_expect_tx(bar, kTile);
             tma_load_4d(smem0 + kSmQ + i * kTile, &tmQ, bar, 0, d[TF_QROW0], 0, d[TF_HEAD0] + i);
           }
-          const int kvh = d[TF_KVH];
+          // shared stages: one K and one V tile per key block; separate stages (p.sep): the
+          // K tiles of the task's heads, then their V tiles
+          const int nld = p.sep ? nt : 1;
+          const int kvh0 = p.sep ? d[TF_HEAD0] / p.q_per_kv : d[TF_KVH];
+          const int kvh1 = p.sep ? (d[TF_HEAD0] + 1) / p.q_per_kv : kvh0;
           const int k_base = d[TF_KSTART];
           for (int jj = 0; jj < nblk && ok; ++jj) {
             const int blk = nblk - 1 - jj;
             // key block -> first row of its 128-row tile (paged: one page is one block)
             const int kv_row = p.page_table ? p.page_table[k_base + blk] * 128 : k_base + blk * 128;
-#pragma unroll
-            for (int which = 0; which < 2; ++which) {
-              if (!ok || !(ok = wait_bar(env, smem_u32(&bars.kv_empty[kv_slot]), kv_ph ^ 1u, 0x10 + kv_slot)))
+            for (int ld = 0; ld < 2 * nld; ++ld) {
+              const int which = ld >= nld, i = which ? ld - nld : ld;
+              if (!(ok = wait_bar(env, smem_u32(&bars.kv_empty[kv_slot]), kv_ph ^ 1u, 0x10 + kv_slot)))
                 break;
               const uint32_t bar = smem_u32(&bars.kv_full[kv_slot]);
               mbar_expect_tx(bar, kTile);
-              tma_load_4d(smem0 + kSmKV + kv_slot * kTile, which ? &tmV : &tmK, bar, 0, kv_row, 0, kvh);
+              tma_load_4d(smem0 + kSmKV + kv_slot * kTile, which ? &tmV : &tmK, bar, 0, kv_row, 0,
+                          i ? kvh1 : kvh0);
               if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
             }
           }
@@ -790,15 +810,27 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
         MA_NEXT_TASK(d, mode)
         MA_DRAIN_IF_SWITCH(mode)
         if (mode == MODE_FA) {
-          const int nblk = d[TF_NBLK];
-          const bool act = mi < d[TF_NT];
+          const int nblk = d[TF_NBLK], nt = d[TF_NT];
+          const bool act = mi < nt;
+          // Shared K/V stages: both issuers follow every slot of the ring.  Separate stages
+          // (p.sep): a key block is nt K slots then nt V slots, issuer mi uses the mi-th of
+          // each group and leaves the others alone (an idle issuer only keeps count).
+          const bool sep = p.sep != 0;
+          const bool walk = act || !sep;
+          auto my_slot = [&](uint32_t& slot, uint32_t& ph) {
+            uint32_t s = kv_slot + (sep ? static_cast<uint32_t>(mi) : 0u), h = kv_ph;
+            if (s >= static_cast<uint32_t>(kKvSlots)) { s -= kKvSlots; h ^= 1u; }
+            slot = s; ph = h;
+            kv_slot += sep ? static_cast<uint32_t>(nt) : 1u;
+            if (kv_slot >= static_cast<uint32_t>(kKvSlots)) { kv_slot -= kKvSlots; kv_ph ^= 1u; }
+          };
           if (act) {
             wait_bar(env, smem_u32(&bars.q_full[mi]), q_par, 0x20 + mi);
             q_par ^= 1u;
           }
-          uint32_t slot_kk = kv_slot;
-          wait_bar(env, smem_u32(&bars.kv_full[slot_kk]), kv_ph, 0x30 + slot_kk);
-          if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
+          uint32_t slot_kk, ph_kk;
+          my_slot(slot_kk, ph_kk);
+          if (walk) wait_bar(env, smem_u32(&bars.kv_full[slot_kk]), ph_kk, 0x30 + slot_kk);
           if (act) {
             tc_fence_after();
             pipe_lock();
@@ -807,11 +839,11 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             pipe_unlock();
             if (nblk == 1) tc_commit(smem_u32(&bars.q_empty[mi]));
           }
-          tc_commit(smem_u32(&bars.kv_empty[slot_kk]));
+          if (walk) tc_commit(smem_u32(&bars.kv_empty[slot_kk]));
           for (int jj = 0; jj < nblk; ++jj) {
-            const uint32_t slot_v = kv_slot;
-            wait_bar(env, smem_u32(&bars.kv_full[slot_v]), kv_ph, 0x40 + slot_v);
-            if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
+            uint32_t slot_v, ph_v;
+            my_slot(slot_v, ph_v);
+            if (walk) wait_bar(env, smem_u32(&bars.kv_full[slot_v]), ph_v, 0x40 + slot_v);
             if (act) {
               if (jj == 0) {   // the previous task's epilogue must have read O out
                 wait_bar(env, smem_u32(&bars.o_free[mi]), (o_uses & 1u) ^ 1u, 0x68 + mi);
@@ -823,9 +855,8 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
             }
             const bool has_next = (jj + 1 < nblk);
             if (has_next) {          // K of the next block: prefetched long ago
-              slot_kk = kv_slot;
-              wait_bar(env, smem_u32(&bars.kv_full[slot_kk]), kv_ph, 0x50 + slot_kk);
-              if (++kv_slot == kKvSlots) { kv_slot = 0; kv_ph ^= 1u; }
+              my_slot(slot_kk, ph_kk);
+              if (walk) wait_bar(env, smem_u32(&bars.kv_full[slot_kk]), ph_kk, 0x50 + slot_kk);
             }
             if (act) {
               pipe_lock();
@@ -841,7 +872,7 @@ fused_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
                 tc_commit(smem_u32(&bars.o_done[mi]));
                 pipe_unlock();
               }
-            } else {
+            } else if (walk) {
               tc_commit(smem_u32(&bars.kv_empty[slot_v]));
               if (has_next) tc_commit(smem_u32(&bars.kv_empty[slot_kk]));
             }

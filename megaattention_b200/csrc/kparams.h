@@ -27,7 +27,9 @@ struct KParams {
   int w_fa, w_oproj, w_ar;
   uint32_t flags;
   float scale_log2;
-  int pair;                       // 1: claim two q heads (same kv head) per FA task
+  int pair;                       // 1: an FA task is two q heads sharing a kv head (q_per_kv even)
+  int sep;                        // 1: an FA task is two q heads, each with K/V stages of its own
+                                  //    (q_per_kv odd, MHA included; the last head of an odd count alone)
   int max_row_tiles, max_owner_slots, max_owner_words;
   unsigned long long wait_limit_ns;
 

@@ -73,6 +73,8 @@ WORKLOADS = {
                    per_rank_seed=True),
     # One long sequence, 8 q / 1 kv heads, hidden 2048, one rank: the tail of the launch is
     # one chain of ever longer attention tasks per head.
+    # c2 with a kv head per q head: attention tasks pair heads that share no K/V.
+    "c2_mha": Workload("c2_mha", _SMALL, 8, 8, 4096, [1]),
     "long16k": Workload("long16k", [16384], 8, 1, 2048, [1]),
     "long32k": Workload("long32k", [32768], 8, 1, 2048, [1]),
 }

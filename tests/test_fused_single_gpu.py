@@ -25,11 +25,36 @@ SENT = -7.0
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 
 
+# Head groupings the fixture matrix does not have: odd q_per_kv (MHA included) with three,
+# six and eight heads, so that attention tasks pair two q heads that do NOT share a kv head
+# (each with K/V stages of its own), plus the single head an odd head count leaves over.
+# Same input recipe as the fixture cases; compared with the oracle only.
+EXTRA_CASES = {
+    "mha_h3":          ([300, 130],      3, 384, 1, None,            31),
+    "q3_h3":           ([200, 64, 130],  3, 256, 3, None,            32),
+    "q3_h6_chunk":     ([260],           6, 256, 3, [516],           33),
+    "mha_h8":          ([300, 200],      8, 512, 1, None,            34),
+    "mha_h1":          ([200],           1, 256, 1, None,            35),
+}
+
+
+def _case_inputs(name):
+    if name in CASES:
+        return CASES[name], make_inputs(name)
+    from cases import _randn
+    sq, H, hidden, qpk, sk, seed = EXTRA_CASES[name]
+    skk = sq if sk is None else sk
+    base = seed * 1000
+    return EXTRA_CASES[name], (_randn((sum(sq), H, 128), base + 0),
+                               _randn((sum(skk), H // qpk, 128), base + 1),
+                               _randn((sum(skk), H // qpk, 128), base + 2),
+                               _randn((H * 128, hidden), base + 3, float(H * 128) ** -0.5))
+
+
 def run_case(name, w=(4, 1, 1), num_ctas=None, launches=1, audit=False):
     from megaattention_b200.metadata import build_row_desc
     from megaattention_b200.runtime import FusedFaOprojArWorkspace
-    sq, H, hidden, qpk, sk, seed = CASES[name]
-    Q, K, V, W = make_inputs(name)
+    (sq, H, hidden, qpk, sk, seed), (Q, K, V, W) = _case_inputs(name)
     meta = build_row_desc(sq, seqlens_k=sk)
     ws = FusedFaOprojArWorkspace.create(
         None, max_num_row_tiles=meta.num_row_tiles, hidden=hidden, H_local=H, D=128,
@@ -70,11 +95,13 @@ def run_case(name, w=(4, 1, 1), num_ctas=None, launches=1, audit=False):
     res["err_rel_fp32"] = err_rel(out, Yp)
     res["err_rel_bf16"] = err_rel(out, Yf)
     res["ctrl"] = ws.ctrl.cpu().numpy().astype(np.int64).tolist()
-    # against the reference-produced fixture as well
-    g = np.load(os.path.join(GOLD, f"chain_{name}.npz"))
-    ref_yf = torch.from_numpy(g["y_final_bits"]).view(torch.bfloat16)
-    res["err_rel_fixture"] = err_rel(out, ref_yf)
     res["err_comp"] = err_beyond_rounding(out, Yp)
+    if name in CASES:       # against the reference-produced fixture as well
+        g = np.load(os.path.join(GOLD, f"chain_{name}.npz"))
+        ref_yf = torch.from_numpy(g["y_final_bits"]).view(torch.bfloat16)
+    else:
+        ref_yf = Yf
+    res["err_rel_fixture"] = err_rel(out, ref_yf)
     res["err_comp_fixture"] = err_beyond_rounding(out, ref_yf, extra_half_ulps=1.0)
     res["q_lt_k"] = sk is not None
     res["out"], res["oscr"], res["Yp"] = out, oscr, Yp
@@ -106,6 +133,17 @@ def test_every_task_runs_exactly_once(name):
     one per launch, over three launches on one workspace, with few CTAs and with all."""
     check(run_case(name, audit=True, launches=3, num_ctas=5))
     check(run_case(name, audit=True))
+
+
+@pytest.mark.parametrize("name", list(EXTRA_CASES))
+def test_heads_that_do_not_share_kv_are_paired_too(name):
+    check(run_case(name))
+    check(run_case(name, launches=3, num_ctas=3))
+
+
+@pytest.mark.parametrize("name", list(EXTRA_CASES))
+def test_unshared_kv_pairs_run_exactly_once(name):
+    check(run_case(name, audit=True, launches=2, num_ctas=5))
 
 
 @pytest.mark.parametrize("w", [(4, 1, 1), (8, 2, 1), (6, 1, 0), (1, 1, 0), (2, 1, 1)])
