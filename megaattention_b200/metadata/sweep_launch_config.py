@@ -30,7 +30,8 @@ if ROOT not in sys.path:
 from megaattention_b200 import _cabi  # noqa: E402
 from megaattention_b200.metadata import build_row_desc, choose_launch_config  # noqa: E402
 from megaattention_b200.metadata.launch_heuristic import (  # noqa: E402
-    choose_launch_config_b200, launch_flags_b200, num_ctas_b200, estimate_work_ratio_kv)
+    choose_launch_config_b200, launch_flags_b200, num_ctas_b200, fa_prime_tiles_b200,
+    estimate_work_ratio_kv)
 from megaattention_b200.workloads import WORKLOADS  # noqa: E402
 
 # (seqlens, H_local, hidden, kv_mult): the reference's twelve shapes ...
@@ -91,7 +92,10 @@ def main():
         torch.cuda.synchronize()
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
 
-        def time_setting(w, flags, ctas, iters):
+        def time_setting(w, flags, ctas, order, iters):
+            if ws.fa_prime_tiles != order:       # claim order of the attention tasks
+                ws.fa_prime_tiles = order
+                ws.set_meta(meta)
             ws._args = _cabi.LaunchArgs(w[0], w[1], w[2] if world > 1 else 0, ctas, 0)
             evs = []
             for i in range(1 + iters):
@@ -116,6 +120,7 @@ def main():
         b200 = choose_launch_config_b200(meta, hidden, world)
         b200_flags = launch_flags_b200(meta, hidden, world, H)
         b200_ctas = num_ctas_b200(meta, hidden, world, H, sms)
+        b200_order = fa_prime_tiles_b200(meta, hidden, world, H)
         name = f"{','.join(map(str, seqlens)) if len(set(seqlens)) > 1 or len(seqlens) < 3 else f'{seqlens[0]}x{len(seqlens)}'}" \
                f"{'' if kvm == 1 else f' k={kvm}q'} h{H} hid{hidden}"
         settings = []
@@ -124,38 +129,44 @@ def main():
                 for ctas in (sms, sms - 4, sms - 16):
                     if ctas != sms and (w != WEIGHTS[0] and w != WEIGHTS[1]):
                         continue
-                    settings.append((w, flags, ctas))
-        k_ref = ("reference default", (ref_cfg.w_fa, ref_cfg.w_oproj, ref_cfg.w_ar), 0, sms)
-        k_b200 = ("b200 choice", (b200.w_fa, b200.w_oproj, b200.w_ar), b200_flags, b200_ctas)
+                    settings.append((w, flags, ctas, 0))
+                # claim orders other than longest-first (long and short row tiles alternating,
+                # 24 short row tiles first) only matter with an AllReduce to feed
+                if world > 1 and w == WEIGHTS[0]:
+                    settings += [(w, flags, sms, -1), (w, flags, sms, 24)]
+        k_ref = ("reference default", (ref_cfg.w_fa, ref_cfg.w_oproj, ref_cfg.w_ar), 0, sms, 0)
+        k_b200 = ("b200 choice", (b200.w_fa, b200.w_oproj, b200.w_ar), b200_flags, b200_ctas,
+                  b200_order)
         # The clock drifts under sustained load, so every setting is timed once per pass, in
         # the same order, over several passes, and the median over the passes is kept.
         samples = {}
         for _ in range(args.passes):
             for key in settings + [k_ref, k_b200]:
-                w, flags, ctas = key[-3:]
-                samples.setdefault(key, []).append(time_setting(w, flags, ctas, args.iters))
+                w, flags, ctas, order = key[-4:]
+                samples.setdefault(key, []).append(time_setting(w, flags, ctas, order, args.iters))
         med = {k: sorted(v)[len(v) // 2] for k, v in samples.items()}
         res = {k: med[k] for k in settings}
         t_ref, t_b200 = med[k_ref], med[k_b200]
         if jf:
             for k in settings:
                 jf.write(json.dumps({"shape": name, "tp": world, "w": k[0], "flags": k[1],
-                                     "ctas": k[2], "ms": res[k], "passes": samples[k]}) + "\n")
+                                     "ctas": k[2], "order": k[3], "ms": res[k],
+                                     "passes": samples[k]}) + "\n")
         best = min(res, key=res.get)
         rows.append((name, estimate_work_ratio_kv(meta, hidden), best, res[best], t_ref, t_b200,
-                     (b200.w_fa, b200.w_oproj, b200.w_ar), b200_flags, b200_ctas))
+                     (b200.w_fa, b200.w_oproj, b200.w_ar), b200_flags, b200_ctas, b200_order))
         if rank == 0:
             print(f"{name}: best {best} {res[best]:.4f} ms, reference default {t_ref:.4f} ms, "
                   f"b200 choice {t_b200:.4f} ms", flush=True)
         del ws, Q, Kt, V, Wo
         torch.cuda.empty_cache()
     if rank == 0:
-        print(f"\n| shape (tp {world}) | r_kv | best (w), flags, CTAs | best ms | reference default ms | "
+        print(f"\n| shape (tp {world}) | r_kv | best (w), flags, CTAs, order | best ms | reference default ms | "
               f"b200 choice | b200 ms | b200 / best |")
         print("|---|---|---|---|---|---|---|---|")
-        for name, r, best, tb, tr, t2, w2, f2, c2 in rows:
-            print(f"| {name} | {r:.2f} | {best[0]}, {best[1]}, {best[2]} | {tb:.4f} | {tr:.4f} | "
-                  f"{w2}, {f2}, {c2} | {t2:.4f} | {t2 / tb:.3f} |")
+        for name, r, best, tb, tr, t2, w2, f2, c2, o2 in rows:
+            print(f"| {name} | {r:.2f} | {best[0]}, {best[1]}, {best[2]}, {best[3]} | {tb:.4f} | {tr:.4f} | "
+                  f"{w2}, {f2}, {c2}, {o2} | {t2:.4f} | {t2 / tb:.3f} |")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
