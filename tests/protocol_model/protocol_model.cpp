@@ -23,6 +23,7 @@
 //                        steps); the others must time out and return, not hang
 //
 // Output: one JSON object on stdout.
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <cstdint>
@@ -42,6 +43,10 @@ enum { MODE_IDLE, MODE_FA, MODE_OPROJ, MODE_AR, MODE_DONE };
 struct Config {
   int tp = 2, ctas = 6, R = 12, H = 4, nsg = 3, launches = 3, limit_ms = 300;
   int drop_rank = -1, drop_slot = -1, strag_rank = -1, strag_ms = 0, leave_rank = -1, leave_from = 0;
+  // attention-task numbering, as in the kernel: 0 = one head per task; 1 = two heads that
+  // share a kv head (H even, the counter steps by 2 over head ids); 2 = two heads without a
+  // shared kv head (the counter numbers tasks, (H + 1) / 2 per row tile, last odd head alone)
+  int pairing = 0;
 };
 
 struct Rank {
@@ -76,10 +81,24 @@ void report(Rank& r, uint32_t code, uint32_t site) {
 }
 
 // ---- the scheduler's three sources (same order of operations as the kernel)
-bool try_fa(Rank& r, int num_fa, int* arg) {
+bool try_fa(Rank& r, const Config& c, int num_fa, int* arg, int* nt) {
+  if (c.pairing == 2) {
+    const int hp = (c.H + 1) >> 1, n_tasks = (num_fa / c.H) * hp;
+    if (static_cast<int>(r.ctrl[C_FA_COUNTER].load(std::memory_order_relaxed)) < n_tasks) {
+      const int id = static_cast<int>(r.ctrl[C_FA_COUNTER].fetch_add(1, std::memory_order_relaxed));
+      if (id < n_tasks) {
+        const int head0 = 2 * (id % hp);
+        *arg = (id / hp) * c.H + head0;
+        *nt = std::min(2, c.H - head0);
+        return true;
+      }
+    }
+    return false;
+  }
+  const uint32_t step = c.pairing == 1 ? 2u : 1u;
   if (static_cast<int>(r.ctrl[C_FA_COUNTER].load(std::memory_order_relaxed)) < num_fa) {
-    const uint32_t id = r.ctrl[C_FA_COUNTER].fetch_add(1, std::memory_order_relaxed);
-    if (static_cast<int>(id) < num_fa) { *arg = static_cast<int>(id); return true; }
+    const uint32_t id = r.ctrl[C_FA_COUNTER].fetch_add(step, std::memory_order_relaxed);
+    if (static_cast<int>(id) < num_fa) { *arg = static_cast<int>(id); *nt = static_cast<int>(step); return true; }
   }
   return false;
 }
@@ -164,11 +183,11 @@ void cta_main(World& w, int rank, int cta) {
                       static_cast<int>(r.ctrl[C_OP_DONE].load(std::memory_order_acquire)) >= total_op &&
                       static_cast<int>(r.ctrl[C_AR_DONE].load(std::memory_order_acquire)) >= local_owned;
     if (done) break;
-    int mode = MODE_IDLE, arg = -1;
+    int mode = MODE_IDLE, arg = -1, nt = 1;
     for (int i = 0; i < 3 && mode == MODE_IDLE; ++i) {
       const int m = 1 + (role + i) % 3;
       bool ok = false;
-      if (m == MODE_FA) ok = try_fa(r, num_fa, &arg);
+      if (m == MODE_FA) ok = try_fa(r, c, num_fa, &arg, &nt);
       else if (m == MODE_OPROJ) ok = try_pop_oproj(r, total_op, &pending, &arg);
       else ok = try_claim_ar(w, rank, &arg);
       if (ok) mode = m;
@@ -181,11 +200,11 @@ void cta_main(World& w, int rank, int cta) {
     }
     idle = false;
     if (mode == MODE_FA) {
-      r.fa_runs[arg].fetch_add(1);
+      for (int i = 0; i < nt; ++i) r.fa_runs[arg + i].fetch_add(1);
       const int ft = arg / c.H;
-      const uint32_t old = r.head_ready[ft].fetch_add(1, std::memory_order_acq_rel);
-      if (static_cast<int>(old) + 1 == c.H) publish_oproj(w, r, ft);
-      r.ctrl[C_FA_DONE].fetch_add(1, std::memory_order_release);
+      const uint32_t old = r.head_ready[ft].fetch_add(static_cast<uint32_t>(nt), std::memory_order_acq_rel);
+      if (static_cast<int>(old) + nt == c.H) publish_oproj(w, r, ft);
+      r.ctrl[C_FA_DONE].fetch_add(static_cast<uint32_t>(nt), std::memory_order_release);
     } else if (mode == MODE_OPROJ) {
       r.op_runs[arg].fetch_add(1);
       const int owner = arg % c.tp, idx = arg / c.tp;
@@ -220,6 +239,7 @@ int main(int argc, char** argv) {
     else if (!strcmp(argv[i], "--tiles")) { c.R = next(1); i += 1; }
     else if (!strcmp(argv[i], "--heads")) { c.H = next(1); i += 1; }
     else if (!strcmp(argv[i], "--nsg")) { c.nsg = next(1); i += 1; }
+    else if (!strcmp(argv[i], "--pairing")) { c.pairing = next(1); i += 1; }
     else if (!strcmp(argv[i], "--launches")) { c.launches = next(1); i += 1; }
     else if (!strcmp(argv[i], "--limit-ms")) { c.limit_ms = next(1); i += 1; }
     else if (!strcmp(argv[i], "--drop-arrival")) { c.drop_rank = next(1); c.drop_slot = next(2); i += 2; }

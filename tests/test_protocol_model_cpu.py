@@ -37,6 +37,18 @@ def test_every_task_runs_exactly_once_and_the_exit_is_clean(model, tp, ctas, til
     assert all(s == [0, 0] for s in out["status"]), out
 
 
+@pytest.mark.parametrize("pairing,heads", [(1, 4), (1, 8), (2, 2), (2, 3), (2, 5), (2, 8)])
+def test_attention_tasks_of_two_heads_count_every_head_once(model, pairing, heads):
+    """The kernel's two-head attention tasks: heads sharing a kv head (the counter steps by
+    two over head ids) and heads that share none (the counter numbers tasks, the last head of
+    an odd count runs alone).  Every (row tile, head) once, the row tile's head count reaches
+    H exactly once, six launches without a reset."""
+    out = model("--tp", 2, "--ctas", 5, "--tiles", 9, "--heads", heads, "--nsg", 3,
+                "--pairing", pairing, "--launches", 6, "--limit-ms", 5000)
+    assert out["launches_ok"] == 6 and out["exactly_once"] and out["clean_exit"], out
+    assert all(s == [0, 0] for s in out["status"]), out
+
+
 def test_a_straggler_rank_is_waited_for(model):
     out = model("--tp", 3, "--launches", 3, "--straggler", 1, 60, "--limit-ms", 3000)
     assert out["launches_ok"] == 3 and out["exactly_once"] and out["clean_exit"], out
