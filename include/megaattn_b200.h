@@ -80,7 +80,10 @@ typedef struct ma_devinfo {
 typedef struct ma_plan_desc {
   int32_t device;
   int32_t tp_size, rank;
-  int32_t H_local, H_kv, D, hidden;
+  int32_t H_local, H_kv, D, hidden;   /* H_local % H_kv == 0; any group size H_local / H_kv:
+                                         an attention task takes two q heads of a row tile,
+                                         sharing the K/V stages when the group size is even,
+                                         with stages of their own otherwise (MHA included) */
   int32_t super_group_n_tiles;
   int32_t max_row_tiles, max_batch, max_tot_q, max_tot_k;
   float softmax_scale;            /* <= 0: D^-0.5                                       */
