@@ -62,8 +62,13 @@ def estimate_work_ratio_kv(meta, hidden: int, N_TILE: int = 128) -> float:
 
 def choose_launch_config_b200(meta, hidden: int, tp_size: int,
                               N_TILE: int = 128) -> LaunchConfig:
-    """Same table, indexed by the KV-aware ratio.  Not part of the reference surface."""
-    row = _TABLE[0] if estimate_work_ratio_kv(meta, hidden, N_TILE) < _R_LO else _TABLE[1]
+    """Same table, indexed by the KV-aware ratio, on one rank.  Not part of the reference
+    surface.  With tp > 1 the balanced row is kept whatever the ratio: in the 8-GPU sweep
+    the attention-heavy row leaves too few CTAs that look for AllReduce work first (k = 4q
+    benchmark shape, tp 8: (8,1,1) 1.115 ms against (2,1,1) 1.099 ms, and 1.061 against
+    1.050 ms with "downstream work first"; on the q = k shapes it is the slowest row)."""
+    kv_heavy = estimate_work_ratio_kv(meta, hidden, N_TILE) >= _R_LO
+    row = _TABLE[1] if (kv_heavy and tp_size <= 1) else _TABLE[0]
     sg = max(1, min(row[2], cdiv(hidden, N_TILE)))
     return LaunchConfig(w_fa=row[0], w_oproj=row[1], w_ar=int(tp_size > 1), sg=sg)
 
@@ -97,10 +102,14 @@ def launch_flags_b200(meta, hidden: int, tp_size: int, H_local: int, D: int = 12
     """Launch flags for the sm_100a kernel (no reference counterpart).
 
     Returns 2 ("drain first": CTAs probe O_proj before attention, AllReduce first on the
-    AllReduce-role CTAs) when the launch is expected to be NVLink bound, else 0.  The
-    estimate compares the un-padded FLOPs at an effective 1.2 PFLOP/s with the AllReduce
-    payload at the ~0.38 TB/s the in-switch reduction sustains on 8 B200s.
+    AllReduce-role CTAs) when the launch is expected to be NVLink bound, and on 8 ranks
+    always, else 0.  The estimate compares the un-padded FLOPs at an effective 1.2 PFLOP/s
+    with the AllReduce payload at the ~0.38 TB/s the in-switch reduction sustains on 8
+    B200s.  Measured: tp 8 — c3 0.648 against 0.672 ms, k = 4q shape (ratio 0.36) 1.050
+    against 1.099 ms; tp 4, c3 (ratio 0.75): 0.944 against 0.940 ms, within noise.
     """
+    if tp_size >= 8:
+        return 2
     return 2 if _allreduce_over_compute(meta, hidden, tp_size, H_local, D) > 0.8 else 0
 
 

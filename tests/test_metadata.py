@@ -131,7 +131,8 @@ def test_kv_aware_ratio_is_additional():
     m = build_row_desc(sq, seqlens_k=[4 * s for s in sq])
     assert estimate_work_ratio_kv(build_row_desc(sq), 4096) == estimate_work_ratio(build_row_desc(sq), 4096)
     assert estimate_work_ratio_kv(m, 4096) > 2.0 > estimate_work_ratio(m, 4096)
-    assert choose_launch_config_b200(m, 4096, 8).w_fa == 8
+    assert choose_launch_config_b200(m, 4096, 1).w_fa == 8
+    assert choose_launch_config_b200(m, 4096, 8).w_fa == 2      # balanced row with an AllReduce to feed
     assert choose_launch_config(m, 4096, 8).w_fa == 2
 
 
