@@ -91,11 +91,14 @@ def fa_prime_tiles_b200(meta, hidden: int, tp_size: int, H_local: int, D: int = 
     """Attention claim order for the sm_100a kernel (``workspace.claim_order``; no reference
     counterpart): 0 = longest row tile first, -1 = long and short row tiles interleaved.
 
-    Interleaved when the AllReduce is a sizeable part of the launch (estimated AllReduce
-    time above half the tensor time): row tiles then finish at an even rate from the start,
-    so O_proj and AllReduce work flows all along instead of piling up behind the attention.
-    Measured on c3: tp 4 0.939 against 0.963 ms; tp 2 (ratio 0.37) no difference."""
-    return -1 if _allreduce_over_compute(meta, hidden, tp_size, H_local, D) > 0.5 else 0
+    Interleaved while O_proj is a sizeable share of the work (KV-aware ratio below the
+    table's switch point): row tiles then finish at an even rate from the start, so O_proj
+    (and AllReduce) work flows all along instead of piling up behind the attention.  Where
+    attention dominates, the longest tasks have to start first and the interleaved order
+    loses.  Measured, interleaved over longest-first: one GPU, ratio < 2 (the benchmark's c2
+    shape, 2048 x 8, 1024 x 4, 4096 x 2): 0.92-0.98; ratio >= 2 (8192 and longer, k = 4q):
+    1.01-1.20; c3 at tp 8: 0.95, tp 4: 0.976, tp 2: 1.004; k = 4q at tp 8: 1.09."""
+    return -1 if estimate_work_ratio_kv(meta, hidden) < _R_LO else 0
 
 
 def launch_flags_b200(meta, hidden: int, tp_size: int, H_local: int, D: int = 128) -> int:

@@ -130,9 +130,9 @@ def main():
                     if ctas != sms and (w != WEIGHTS[0] and w != WEIGHTS[1]):
                         continue
                     settings.append((w, flags, ctas, 0))
-                # claim orders other than longest-first (long and short row tiles alternating,
-                # 24 short row tiles first) only matter with an AllReduce to feed
-                if world > 1 and w == WEIGHTS[0]:
+                # claim orders other than longest-first: long and short row tiles alternating,
+                # 24 short row tiles first
+                if w == WEIGHTS[0]:
                     settings += [(w, flags, sms, -1), (w, flags, sms, 24)]
         k_ref = ("reference default", (ref_cfg.w_fa, ref_cfg.w_oproj, ref_cfg.w_ar), 0, sms, 0)
         k_b200 = ("b200 choice", (b200.w_fa, b200.w_oproj, b200.w_ar), b200_flags, b200_ctas,

@@ -160,3 +160,23 @@ def test_claim_order_is_longest_first_with_optional_priming():
     mixed = claim_order(meta, prime=-1)          # longest, shortest, 2nd longest, ...
     assert sorted(mixed.tolist()) == list(range(meta.num_row_tiles))
     assert mixed[0] == order[0] and mixed[1] == order[-1] and mixed[2] == order[1]
+
+
+def test_b200_launch_choices_for_the_benchmark_shapes():
+    """The additional B200 entry points are deterministic functions of the batch: downstream
+    work first on 8 ranks and where the AllReduce dominates, interleaved claim order while
+    O_proj is a sizeable share of the work, the balanced role row whenever there is an
+    AllReduce to feed.  Values as calibrated by metadata/sweep_launch_config.py."""
+    from megaattention_b200.metadata.launch_heuristic import (
+        fa_prime_tiles_b200, launch_flags_b200)
+    from megaattention_b200.workloads import WORKLOADS
+    want = {("c2", 1): (0, -1, 2), ("c3", 1): (0, -1, 2), ("c3", 2): (0, -1, 2), ("c3", 4): (0, -1, 2),
+            ("c3", 8): (2, -1, 2), ("c4", 8): (2, -1, 2), ("c5", 8): (2, 0, 2),
+            ("long16k", 1): (0, 0, 8), ("long32k", 1): (0, 0, 8)}
+    for (name, tp), (flags, order, w_fa) in want.items():
+        wl = WORKLOADS[name]
+        h, _ = wl.heads_local(tp)
+        m = build_row_desc(wl.seqlens_q, seqlens_k=wl.seqlens_k)
+        got = (launch_flags_b200(m, wl.hidden, tp, h), fa_prime_tiles_b200(m, wl.hidden, tp, h),
+               choose_launch_config_b200(m, wl.hidden, tp).w_fa)
+        assert got == (flags, order, w_fa), (name, tp, got)
