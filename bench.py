@@ -377,7 +377,7 @@ def main():
                     "peak_source": peaks["source"]}
     roofline.update({
         # dram read+write bytes of one launch from an ncu capture (profiles/): c2, tp 1 only
-        "traffic": 146.2e6 if (wl.name == "c2" and tp == 1 and args.stage == "fused") else None,
+        "traffic": 141.9e6 if (wl.name == "c2" and tp == 1 and args.stage == "fused") else None,
         "traffic_unit": "bytes/launch",
         "tensor_tflops": tensor_achieved, "tensor_frac_of_measured": tensor_achieved / peaks["tflops"],
         "tensor_frac_of_nominal": tensor_achieved / TENSOR_TFLOPS_NOMINAL,
