@@ -22,14 +22,14 @@ ships no code for it.  The contract built here:
 * many layers share one workspace (the kernel's exit path leaves the control state clean,
   so there is no host reset between layers);
 * the launch flags and the attention claim order are chosen per step from the batch at hand
-  (``launch_flags_b200``, ``fa_prime_tiles_b200``) unless the caller passes ``flags``.
+  by the workspace (``launch_flags_b200``, ``fa_prime_tiles_b200``) unless the caller passes
+  ``flags`` or pins ``ws.default_flags`` / ``ws.fa_prime_tiles``.
 """
 from __future__ import annotations
 
 import numpy as np
 import torch
 
-from ..metadata.launch_heuristic import fa_prime_tiles_b200, launch_flags_b200
 from ..metadata.row_desc import build_row_desc
 
 
@@ -87,9 +87,6 @@ class FusedPrefillLayer:
                 "page_table / cache_seqlens need a workspace created with paged=True"
             lens_k = lens_q if cu_seqlens_k is None else _seqlens(cu_seqlens_k)
         meta = build_row_desc(lens_q, seqlens_k=lens_k)      # asserts 0 < q_len <= k_len
-        if flags is None:
-            flags = ws.default_flags | launch_flags_b200(meta, ws.hidden, ws.tp_size, ws.H_local)
-            ws.fa_prime_tiles = fa_prime_tiles_b200(meta, ws.hidden, ws.tp_size, ws.H_local)
         ws.bind_inputs(meta, q, k, v, self.W_o, page_table=page_table, cache_seqlens=cache_seqlens)
         ws.launch(flags)
         self.meta = meta

@@ -25,6 +25,7 @@ import numpy as np
 import torch
 
 from .. import _cabi
+from ..metadata.launch_heuristic import fa_prime_tiles_b200, launch_flags_b200
 from ..metadata.row_desc import active_counts, oproj_task_counts
 
 NUM_CTRL = 8
@@ -72,9 +73,13 @@ class FusedFaOprojArWorkspace:
         self._lib = _cabi.lib
         self._args = None
         self._meta = None
-        self.default_flags = 0   # OR of _cabi.MA_FLAG_* applied by launch()
+        # Launch flags applied by launch() (OR of _cabi.MA_FLAG_*) and attention claim order
+        # (see claim_order).  None = chosen for the batch at hand by the calibrated rules,
+        # launch_flags_b200 / fa_prime_tiles_b200; an int pins the setting.
+        self.default_flags = None
+        self.fa_prime_tiles = None
+        self._auto_flags = 0
         self.ar_p2p = True       # tp_size == 2: AllReduce through peer loads instead of multimem
-        self.fa_prime_tiles = 0  # see claim_order
 
     # ------------------------------------------------------------------ create
     @classmethod
@@ -374,8 +379,12 @@ class FusedFaOprojArWorkspace:
             slot[1].synchronize()
         buf = slot[0].numpy()
         o = self._meta_offs
+        prime = self.fa_prime_tiles
+        if prime is None:
+            prime = fa_prime_tiles_b200(meta, self.hidden, self.tp_size, self.H_local)
+        self._auto_flags = launch_flags_b200(meta, self.hidden, self.tp_size, self.H_local)
         for i, arr in enumerate((meta.cu_seqlens_q, meta.cu_seqlens_k, meta.batch_idx, meta.m_block,
-                                 claim_order(meta, self.fa_prime_tiles),
+                                 claim_order(meta, prime),
                                  active_counts(R, self.H_local, self.num_super_groups,
                                                self.tp_size, self.rank))):
             arr = np.asarray(arr, dtype=np.int32)
@@ -390,7 +399,8 @@ class FusedFaOprojArWorkspace:
 
     def launch(self, flags=None):
         assert self._plan is not None, "call compile() first"
-        flags = self.default_flags if flags is None else flags
+        if flags is None:
+            flags = self._auto_flags if self.default_flags is None else self.default_flags
         if self.tp_size == 2 and self.ar_p2p:
             # two GPUs: reduce with peer loads/stores, not multimem (see MA_FLAG_AR_P2P)
             flags |= _cabi.MA_FLAG_AR_P2P
