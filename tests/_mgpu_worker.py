@@ -35,25 +35,25 @@ def rnd(shape, seed, std=1.0):
     return (torch.randn(shape, generator=g) * std).to(torch.bfloat16)
 
 
-def inputs(layer, rank, sq, sk):
-    s = 7000 + layer * 100 + rank * 10
-    hkv = H // QPK
-    return (rnd((sum(sq), H, 128), s), rnd((sum(sk), hkv, 128), s + 1),
-            rnd((sum(sk), hkv, 128), s + 2), rnd((H * 128, HIDDEN), s + 3, (H * 128) ** -0.5))
+def inputs(layer, rank, sq, sk, h=H, qpk=QPK):
+    s = 7000 + layer * 100 + rank * 10 + (0 if (h, qpk) == (H, QPK) else 50000)
+    hkv = h // qpk
+    return (rnd((sum(sq), h, 128), s), rnd((sum(sk), hkv, 128), s + 1),
+            rnd((sum(sk), hkv, 128), s + 2), rnd((h * 128, HIDDEN), s + 3, (h * 128) ** -0.5))
 
 
-def run_layers(ws, rank, world, dev, tag):
+def run_layers(ws, rank, world, dev, tag, layers=None, h=H, qpk=QPK):
     worst = 0.0
-    for li, (sq, sk) in enumerate(LAYERS):
+    for li, (sq, sk) in enumerate(LAYERS if layers is None else layers):
         sk = sq if sk is None else sk
         meta = build_row_desc(sq, seqlens_k=sk)
-        mine = inputs(li, rank, sq, sk)
+        mine = inputs(li, rank, sq, sk, h, qpk)
         ws.set_layer(meta, *[t.to(dev) for t in mine])
         ws.launch()
         ws.check_status()
         acc, parts = None, []
         for r in range(world):
-            Q, K, V, W = inputs(li, r, sq, sk)
+            Q, K, V, W = inputs(li, r, sq, sk, h, qpk)
             yp = oproj_oracle(fa_oracle(Q, K, V, sq, sk), W)
             parts.append(yp)
             acc = yp.clone() if acc is None else acc + yp
@@ -155,6 +155,15 @@ def main():
     meta = build_row_desc(sq)
     ws.set_layer(meta, *[t.to(dev) for t in inputs(2, rank, sq, sq)])
     ws.launch(); ws.check_status()
+    dist.barrier()
+    # Three q heads with a kv head each per rank: attention tasks pair heads that share no
+    # K/V stages and the third head runs alone; flags and claim order are left to the
+    # workspace's own choice for each batch.
+    ws3 = FusedFaOprojArWorkspace.create(
+        group, MAX_RT, HIDDEN, 3, 128, tp_size=world, rank=rank, super_group_n_tiles=SG,
+        q_per_kv=1, max_tot_k=1536, device=dev)
+    ws3.compile(w_fa=2, w_oproj=1, w_ar=1, num_ctas=int(os.environ.get("MA_TEST_CTAS", "24")))
+    worst = max(worst, run_layers(ws3, rank, world, dev, "mha h3", layers=LAYERS[:8], h=3, qpk=1))
     dist.barrier()
     if os.environ.get("MA_TEST_C3", "1") == "1":
         for flags in (0, _cabi.MA_FLAG_DRAIN_FIRST):
