@@ -232,6 +232,33 @@ typedef struct ma_noalloc_args {
 
 int ma_fused_prefill_noalloc(const ma_noalloc_args* args, void* stream);
 
+/*
+ * Consumer of the fused launch's output: residual add + RMSNorm, read straight from the
+ * tile-padded csym buffer.  The reference lists this op as the next one after its fused
+ * kernel (README.md:41-44 of the reference, "residual / RMSNorm consumer") and has no code
+ * or interface for it, so the entry point mirrors nothing; the arithmetic is
+ *   h   = bf16( float(y) + float(residual) )            (the residual stream, rounded once)
+ *   out = bf16( float(h) * rsqrt(mean(float(h)^2) + eps) * float(weight) )
+ * per token row over `hidden` columns.  Token row i of sequence b is row (i % 128) of row
+ * tile (first tile of b) + i / 128 in csym; cu_q / fa_b / fa_mb are the plan's device arrays
+ * of the launch that produced csym.  All pointers are device addresses, 16-byte aligned;
+ * hidden % 8 == 0, hidden <= 16384 (MA_ERR_CAPACITY beyond); row_pitch = csym's row pitch in
+ * elements (num_out * 128).  residual_out may be residual_in (in place).  Asynchronous on
+ * `stream`; no allocation, no synchronisation.
+ */
+typedef struct ma_rmsnorm_args {
+  uint64_t csym;           /* bf16 [num_row_tiles, 128, row_pitch]                     */
+  uint64_t residual_in;    /* bf16 [tot_q, hidden]                                     */
+  uint64_t weight;         /* bf16 [hidden]                                            */
+  uint64_t residual_out;   /* bf16 [tot_q, hidden]                                     */
+  uint64_t normed_out;     /* bf16 [tot_q, hidden]                                     */
+  uint64_t cu_q, fa_b, fa_mb;   /* i32 device arrays, as in ma_plan_desc               */
+  int32_t num_row_tiles, hidden, row_pitch;
+  float eps;
+} ma_rmsnorm_args;
+
+int ma_residual_rmsnorm(const ma_rmsnorm_args* args, void* stream);
+
 const char* ma_strerror(int code);
 
 #ifdef __cplusplus

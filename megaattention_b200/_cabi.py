@@ -27,7 +27,7 @@ MA_ERR_DEVICE_TIMEOUT = -4
 MA_ERR_CAPACITY = -5
 
 EXPORTS = ("ma_query_device", "ma_plan_create", "ma_launch", "ma_plan_set_inputs", "ma_read_status",
-           "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc")
+           "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc", "ma_residual_rmsnorm")
 
 MA_NOALLOC_OSCRATCH_BYTES = 16 << 20
 MA_NOALLOC_MAX_BATCH = 512
@@ -83,6 +83,14 @@ class NoAllocArgs(C.Structure):
                 ("out", C.c_uint64), ("status_out", C.POINTER(Status))]
 
 
+class RmsNormArgs(C.Structure):
+    _fields_ = [("csym", C.c_uint64), ("residual_in", C.c_uint64), ("weight", C.c_uint64),
+                ("residual_out", C.c_uint64), ("normed_out", C.c_uint64),
+                ("cu_q", C.c_uint64), ("fa_b", C.c_uint64), ("fa_mb", C.c_uint64),
+                ("num_row_tiles", C.c_int32), ("hidden", C.c_int32), ("row_pitch", C.c_int32),
+                ("eps", C.c_float)]
+
+
 def _load(path=None, audit=False):
     path = path or (_build.LIB_AUDIT if audit else _build.LIB)
     if not os.path.exists(path) or _build._stale(path):
@@ -108,6 +116,8 @@ def _load(path=None, audit=False):
     lib.ma_plan_destroy.restype = None
     lib.ma_fused_prefill_noalloc.argtypes = [C.POINTER(NoAllocArgs), C.c_void_p]
     lib.ma_fused_prefill_noalloc.restype = C.c_int
+    lib.ma_residual_rmsnorm.argtypes = [C.POINTER(RmsNormArgs), C.c_void_p]
+    lib.ma_residual_rmsnorm.restype = C.c_int
     lib.ma_strerror.argtypes = [C.c_int]
     lib.ma_strerror.restype = C.c_char_p
     return lib

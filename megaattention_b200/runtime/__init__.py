@@ -5,3 +5,4 @@ from .workspace import FusedFaOprojArWorkspace
 from .prefill_layer import FusedPrefillLayer
 
 __all__ = ["FusedFaOprojArWorkspace", "FusedPrefillLayer"]
+from .residual_rmsnorm import residual_rmsnorm  # noqa: F401

@@ -19,7 +19,8 @@ def _declared_functions():
 def test_every_declared_symbol_is_exported():
     names = _declared_functions()
     assert {"ma_query_device", "ma_plan_create", "ma_launch", "ma_read_status",
-            "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc"} <= set(names)
+            "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc",
+            "ma_residual_rmsnorm"} <= set(names)
     for n in names:
         assert getattr(_cabi.lib, n) is not None, n
     assert set(names) == set(_cabi.EXPORTS)
@@ -38,6 +39,7 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(_cabi.PlanDesc) == 56 + 21 * 8 + 3 * 64 + 32 + 64 + 8
     assert _cabi.NoAllocArgs.seqlens_q.offset == 40
     assert C.sizeof(_cabi.NoAllocArgs) == 40 + 2 * 8 + 5 * 8 + 8
+    assert _cabi.RmsNormArgs.num_row_tiles.offset == 64 and C.sizeof(_cabi.RmsNormArgs) == 80
 
 
 def test_error_strings_and_null_arguments():
@@ -80,7 +82,7 @@ def test_ctypes_mirror_agrees_with_the_compiled_header(tmp_path):
     assert cc, "a C compiler is part of the build environment"
     pairs = {"ma_devinfo": _cabi.DevInfo, "ma_plan_desc": _cabi.PlanDesc,
              "ma_launch_args": _cabi.LaunchArgs, "ma_status": _cabi.Status,
-             "ma_noalloc_args": _cabi.NoAllocArgs}
+             "ma_noalloc_args": _cabi.NoAllocArgs, "ma_rmsnorm_args": _cabi.RmsNormArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>',
              '#include "%s"' % os.path.join(ROOT, "include", "megaattn_b200.h"),
              'int main(void) {']
@@ -102,3 +104,24 @@ def test_ctypes_mirror_agrees_with_the_compiled_header(tmp_path):
         assert int(val) == want, (cname, fname, val, want)
         seen += 1
     assert seen == sum(len(ct._fields_) + 1 for ct in pairs.values())
+
+
+def test_consumer_entry_point_validates_before_any_device_call():
+    """ma_residual_rmsnorm: null, misaligned and over-wide arguments are refused on the host
+    (this machine has no GPU: anything that reached CUDA would fail differently)."""
+    ok = dict(csym=1 << 20, residual_in=2 << 20, weight=3 << 20, residual_out=2 << 20,
+              normed_out=4 << 20, cu_q=5 << 20, fa_b=6 << 20, fa_mb=7 << 20,
+              num_row_tiles=3, hidden=4096, row_pitch=4096, eps=1e-6)
+
+    def call(**kw):
+        a = _cabi.RmsNormArgs(**{**ok, **kw})
+        return _cabi.lib.ma_residual_rmsnorm(C.byref(a), None)
+
+    assert _cabi.lib.ma_residual_rmsnorm(None, None) == _cabi.MA_ERR_INVALID
+    assert call(weight=0) == _cabi.MA_ERR_INVALID
+    assert call(normed_out=(4 << 20) + 8) == _cabi.MA_ERR_INVALID          # 16-byte accesses
+    assert call(hidden=4100) == _cabi.MA_ERR_INVALID                       # not a multiple of 8
+    assert call(row_pitch=2048) == _cabi.MA_ERR_INVALID                    # narrower than hidden
+    assert call(eps=-1.0) == _cabi.MA_ERR_INVALID
+    assert call(hidden=16392, row_pitch=16392) == _cabi.MA_ERR_CAPACITY
+    assert call(num_row_tiles=0) == _cabi.MA_OK                            # nothing to do
