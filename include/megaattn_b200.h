@@ -259,6 +259,28 @@ typedef struct ma_rmsnorm_args {
 
 int ma_residual_rmsnorm(const ma_rmsnorm_args* args, void* stream);
 
+/*
+ * Producer-side op: rotary position embedding, in place, on the packed varlen Q
+ * [tot_q, H_local, 128] and on the new rows of K [tot_k, H_kv, 128] (contiguous layout),
+ * before the fused launch reads them.  The reference lists the "QKV-proj / RoPE producer"
+ * as a step it has not built (README.md:41-44 of the reference): no interface to mirror.
+ * Rotate-half convention with the 64 frequencies inv_freq[d] (fp32, e.g. theta^(-d/64)),
+ * fp32 angles and products, one rounding.  Query row i of sequence b has position (k_len_b - q_len_b) + i; the K rows
+ * rotated are the last q_len_b rows of sequence b (with a cached prefix, the prefix was
+ * rotated when it was written).  token_batch[i] is the sequence of packed query row i.
+ * Device addresses; q and k 16-byte aligned; asynchronous on `stream`.
+ */
+typedef struct ma_rope_args {
+  uint64_t q, k;                    /* bf16, rotated in place                           */
+  uint64_t cu_q, cu_k;              /* i32 [num_batch + 1]                              */
+  uint64_t token_batch;             /* i32 [tot_q]                                      */
+  uint64_t inv_freq;                /* f32 [64]                                         */
+  int32_t tot_q, H_local, H_kv;
+  int32_t reserved0;
+} ma_rope_args;
+
+int ma_rope_qk(const ma_rope_args* args, void* stream);
+
 const char* ma_strerror(int code);
 
 #ifdef __cplusplus

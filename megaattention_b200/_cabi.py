@@ -27,7 +27,7 @@ MA_ERR_DEVICE_TIMEOUT = -4
 MA_ERR_CAPACITY = -5
 
 EXPORTS = ("ma_query_device", "ma_plan_create", "ma_launch", "ma_plan_set_inputs", "ma_read_status",
-           "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc", "ma_residual_rmsnorm")
+           "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc", "ma_residual_rmsnorm", "ma_rope_qk")
 
 MA_NOALLOC_OSCRATCH_BYTES = 16 << 20
 MA_NOALLOC_MAX_BATCH = 512
@@ -91,6 +91,12 @@ class RmsNormArgs(C.Structure):
                 ("eps", C.c_float)]
 
 
+class RopeArgs(C.Structure):
+    _fields_ = [("q", C.c_uint64), ("k", C.c_uint64), ("cu_q", C.c_uint64), ("cu_k", C.c_uint64),
+                ("token_batch", C.c_uint64), ("inv_freq", C.c_uint64), ("tot_q", C.c_int32),
+                ("H_local", C.c_int32), ("H_kv", C.c_int32), ("reserved0", C.c_int32)]
+
+
 def _load(path=None, audit=False):
     path = path or (_build.LIB_AUDIT if audit else _build.LIB)
     if not os.path.exists(path) or _build._stale(path):
@@ -118,6 +124,8 @@ def _load(path=None, audit=False):
     lib.ma_fused_prefill_noalloc.restype = C.c_int
     lib.ma_residual_rmsnorm.argtypes = [C.POINTER(RmsNormArgs), C.c_void_p]
     lib.ma_residual_rmsnorm.restype = C.c_int
+    lib.ma_rope_qk.argtypes = [C.POINTER(RopeArgs), C.c_void_p]
+    lib.ma_rope_qk.restype = C.c_int
     lib.ma_strerror.argtypes = [C.c_int]
     lib.ma_strerror.restype = C.c_char_p
     return lib

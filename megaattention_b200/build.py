@@ -13,7 +13,7 @@ LIB = os.path.join(HERE, "libmegaattn_b200.so")
 # never-taken branch in the scheduler role shifts the attention loop's code generation
 # (measured: +1.2 % on the attention stage).
 LIB_AUDIT = os.path.join(HERE, "libmegaattn_b200_audit.so")
-SOURCES = ["fused_prefill.cu", "cabi.cu", "noalloc.cu", "residual_rmsnorm.cu"]
+SOURCES = ["fused_prefill.cu", "cabi.cu", "noalloc.cu", "residual_rmsnorm.cu", "rope.cu"]
 HEADERS = ["ptx.cuh", "kparams.h", os.path.join("..", "..", "include", "megaattn_b200.h")]
 
 

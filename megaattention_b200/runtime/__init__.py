@@ -4,5 +4,7 @@ reference only sketches in its design notes."""
 from .workspace import FusedFaOprojArWorkspace
 from .prefill_layer import FusedPrefillLayer
 
-__all__ = ["FusedFaOprojArWorkspace", "FusedPrefillLayer"]
-from .residual_rmsnorm import residual_rmsnorm  # noqa: F401
+from .residual_rmsnorm import residual_rmsnorm
+from .rope import rope_qk_
+
+__all__ = ["FusedFaOprojArWorkspace", "FusedPrefillLayer", "residual_rmsnorm", "rope_qk_"]

@@ -20,7 +20,7 @@ def test_every_declared_symbol_is_exported():
     names = _declared_functions()
     assert {"ma_query_device", "ma_plan_create", "ma_launch", "ma_read_status",
             "ma_plan_destroy", "ma_strerror", "ma_fused_prefill_noalloc",
-            "ma_residual_rmsnorm"} <= set(names)
+            "ma_residual_rmsnorm", "ma_rope_qk"} <= set(names)
     for n in names:
         assert getattr(_cabi.lib, n) is not None, n
     assert set(names) == set(_cabi.EXPORTS)
@@ -82,7 +82,8 @@ def test_ctypes_mirror_agrees_with_the_compiled_header(tmp_path):
     assert cc, "a C compiler is part of the build environment"
     pairs = {"ma_devinfo": _cabi.DevInfo, "ma_plan_desc": _cabi.PlanDesc,
              "ma_launch_args": _cabi.LaunchArgs, "ma_status": _cabi.Status,
-             "ma_noalloc_args": _cabi.NoAllocArgs, "ma_rmsnorm_args": _cabi.RmsNormArgs}
+             "ma_noalloc_args": _cabi.NoAllocArgs, "ma_rmsnorm_args": _cabi.RmsNormArgs,
+             "ma_rope_args": _cabi.RopeArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>',
              '#include "%s"' % os.path.join(ROOT, "include", "megaattn_b200.h"),
              'int main(void) {']
@@ -125,3 +126,19 @@ def test_consumer_entry_point_validates_before_any_device_call():
     assert call(eps=-1.0) == _cabi.MA_ERR_INVALID
     assert call(hidden=16392, row_pitch=16392) == _cabi.MA_ERR_CAPACITY
     assert call(num_row_tiles=0) == _cabi.MA_OK                            # nothing to do
+
+
+def test_rope_entry_point_validates_before_any_device_call():
+    ok = dict(q=1 << 20, k=2 << 20, cu_q=3 << 20, cu_k=4 << 20, token_batch=5 << 20,
+              inv_freq=6 << 20, tot_q=10, H_local=8, H_kv=1, reserved0=0)
+
+    def call(**kw):
+        a = _cabi.RopeArgs(**{**ok, **kw})
+        return _cabi.lib.ma_rope_qk(C.byref(a), None)
+
+    assert _cabi.lib.ma_rope_qk(None, None) == _cabi.MA_ERR_INVALID
+    assert call(inv_freq=0) == _cabi.MA_ERR_INVALID
+    assert call(q=(1 << 20) + 2) == _cabi.MA_ERR_INVALID                   # 16-byte accesses
+    assert call(H_kv=0) == _cabi.MA_ERR_INVALID
+    assert call(tot_q=-1) == _cabi.MA_ERR_INVALID
+    assert call(tot_q=0) == _cabi.MA_OK                                    # nothing to do
