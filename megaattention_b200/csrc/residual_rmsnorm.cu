@@ -36,22 +36,23 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
   return v;
 }
 
-// NCH: 16-byte chunks per thread (hidden <= NCH * 256 * 8).  The widest form keeps 64
-// registers of row and weight values, so it runs two CTAs per SM instead of four.
-template <int NCH>
-__global__ void __launch_bounds__(kRnThreads, NCH >= 8 ? 2 : 4)
+// NCH: 16-byte chunks per thread, T: threads per CTA (hidden <= NCH * T * 8).  Rows wider
+// than 8192 columns take 512 threads with four chunks each (two CTAs per SM) rather than
+// 256 threads with eight: the latter needs 126 registers for the row and weight values.
+template <int NCH, int T>
+__global__ void __launch_bounds__(T, 1024 / T)
 residual_rmsnorm_kernel(const uint16_t* __restrict__ csym, const uint16_t* res_in,
                         const uint16_t* __restrict__ weight, uint16_t* res_out,
                         uint16_t* __restrict__ normed, const int* __restrict__ cu_q,
                         const int* __restrict__ fa_b, const int* __restrict__ fa_mb,
                         int num_row_tiles, int hidden, int row_pitch, float eps) {
-  __shared__ float s_part[2][kRnThreads / 32];
+  __shared__ float s_part[2][T / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nchunk = hidden >> 3;
   uint4 w[NCH];
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
-    const int c = tid + k * kRnThreads;
+    const int c = tid + k * T;
     w[k] = (c < nchunk) ? reinterpret_cast<const uint4*>(weight)[c] : make_uint4(0, 0, 0, 0);
   }
   const float inv_n = 1.f / static_cast<float>(hidden);
@@ -69,7 +70,7 @@ residual_rmsnorm_kernel(const uint16_t* __restrict__ csym, const uint16_t* res_i
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
-      const int c = tid + k * kRnThreads;
+      const int c = tid + k * T;
       if (c < nchunk) {
         const uint4 a = ld_stream(y4 + c), d = ld_stream(r4 + c);
         const uint32_t av[4] = {a.x, a.y, a.z, a.w}, dv[4] = {d.x, d.y, d.z, d.w};
@@ -93,11 +94,11 @@ residual_rmsnorm_kernel(const uint16_t* __restrict__ csym, const uint16_t* res_i
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int i = 0; i < kRnThreads / 32; ++i) tot += part[i];
+    for (int i = 0; i < T / 32; ++i) tot += part[i];
     const float rstd = rsqrtf(tot * inv_n + eps);
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
-      const int c = tid + k * kRnThreads;
+      const int c = tid + k * T;
       if (c < nchunk) {
         const uint32_t hv[4] = {h[k].x, h[k].y, h[k].z, h[k].w};
         const uint32_t wv[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
@@ -122,7 +123,7 @@ extern "C" int ma_residual_rmsnorm(const ma_rmsnorm_args* a, void* stream) {
   if (a->num_row_tiles < 0 || a->hidden <= 0 || (a->hidden & 7) || a->row_pitch < a->hidden ||
       (a->row_pitch & 7) || !(a->eps >= 0.f))
     return MA_ERR_INVALID;
-  if (a->hidden > 8 * ma::kRnThreads * 8) return MA_ERR_CAPACITY;      // 16384 columns
+  if (a->hidden > 4 * 512 * 8) return MA_ERR_CAPACITY;                 // 16384 columns
   const uint64_t ptrs[] = {a->csym, a->residual_in, a->weight, a->residual_out, a->normed_out};
   for (uint64_t p : ptrs)
     if (p & 15u) return MA_ERR_INVALID;                                // 16-byte accesses
@@ -132,21 +133,23 @@ extern "C" int ma_residual_rmsnorm(const ma_rmsnorm_args* a, void* stream) {
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return MA_ERR_CUDA;
   const int rows = a->num_row_tiles * 128;
-  const int nch = (a->hidden / 8 + ma::kRnThreads - 1) / ma::kRnThreads;
-  const int per_sm = nch > 4 ? 2 : 4;
+  const int nchunk = a->hidden / 8;
+  const int threads = nchunk > 4 * ma::kRnThreads ? 2 * ma::kRnThreads : ma::kRnThreads;
+  const int nch = (nchunk + threads - 1) / threads;
+  const int per_sm = 1024 / threads;
   const int grid = rows < sms * per_sm ? rows : sms * per_sm;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define MA_RN_LAUNCH(N)                                                                          \
-  ma::residual_rmsnorm_kernel<N><<<grid, ma::kRnThreads, 0, st>>>(                              \
+#define MA_RN_LAUNCH(N, T)                                                                       \
+  ma::residual_rmsnorm_kernel<N, T><<<grid, T, 0, st>>>(                                        \
       reinterpret_cast<const uint16_t*>(a->csym), reinterpret_cast<const uint16_t*>(a->residual_in), \
       reinterpret_cast<const uint16_t*>(a->weight), reinterpret_cast<uint16_t*>(a->residual_out),   \
       reinterpret_cast<uint16_t*>(a->normed_out), reinterpret_cast<const int*>(a->cu_q),           \
       reinterpret_cast<const int*>(a->fa_b), reinterpret_cast<const int*>(a->fa_mb),               \
       a->num_row_tiles, a->hidden, a->row_pitch, a->eps)
-  if (nch <= 1) MA_RN_LAUNCH(1);
-  else if (nch <= 2) MA_RN_LAUNCH(2);
-  else if (nch <= 4) MA_RN_LAUNCH(4);
-  else MA_RN_LAUNCH(8);
+  if (threads == 2 * ma::kRnThreads) MA_RN_LAUNCH(4, 512);
+  else if (nch <= 1) MA_RN_LAUNCH(1, 256);
+  else if (nch <= 2) MA_RN_LAUNCH(2, 256);
+  else MA_RN_LAUNCH(4, 256);
 #undef MA_RN_LAUNCH
   return cudaGetLastError() == cudaSuccess ? MA_OK : MA_ERR_CUDA;
 }
