@@ -52,6 +52,7 @@ def rope_qk_(q, k, cu_seqlens_q=None, cu_seqlens_k=None, *, theta: float = 10000
     assert q.dim() == 3 and k.dim() == 3 and q.shape[2] == 128 and k.shape[2] == 128
     assert q.is_contiguous() and k.is_contiguous()
     dev = q.device
+    assert meta is not None or cu_seqlens_q is not None, "pass cu_seqlens_q (and _k) or meta=rope_meta(...)"
     meta_d, nb, tot_q, tot_k = meta if meta is not None else rope_meta(cu_seqlens_q, cu_seqlens_k, dev)
     assert tot_q == q.shape[0] and tot_k == k.shape[0] and meta_d.device == dev
     w = default_inv_freq(theta, dev) if inv_freq is None else inv_freq.to(dev, torch.float32).contiguous()
